@@ -1,0 +1,332 @@
+// Gated delta rule: a recurrent mixer whose state is one matrix per head, S [dim][vdim] in 32-bit, with short
+// causal convolutions in front of it.
+//
+//   x = [W_q h ; W_k h ; W_v h]                         the projected row of a token, C = 2 Gq dim + H vdim channels
+//   y_c(t) = silu(sum_i w[c][i] x_c(t - taps + 1 + i))  per channel, zeros before the start of the sequence
+//   q, k: per query/key head, y / sqrt(sum(y^2) + 1e-6); q also times dim^(-1/2); v = y
+//   beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h]))            one of each per head and token
+//   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q                       (head h uses q/k head h / (H / Gq))
+//   out = o / sqrt(mean(o^2) + eps) * norm_w * silu(z)                                   per head over vdim
+//
+// The state of a request is one float row per layer: S [H][dim][vdim], then the last taps - 1 projected rows
+// [taps - 1][C] (oldest first).  A state slot of -1 starts from zeros and stores nothing.  Everything after the
+// projections is 32-bit; a request's result does not depend on how it was cut into steps, because every token's
+// arithmetic is the same chain whatever the step brought before it.
+//
+// The recurrence is evaluated in the equivalent form
+//   P1 = S^T k, P2 = S^T q (old state), u = beta (v - g P1), o = g P2 + u (k . q), S <- g S + k u^T,
+// which needs one pass over the state for the two products and one for the update.
+#include "common.cuh"
+#include <math.h>
+
+// ---------------------------------------------------------------- convolution, silu, unit vectors
+// One block per (token, segment); a segment is one q head, one k head (dim channels, made a unit vector) or one v head
+// (vdim channels).  The taps before the step's first token of the request come from the state.
+template <typename TI>
+__global__ void __launch_bounds__(128)
+delta_conv_kernel(const TI* __restrict__ x, long x_stride, const float* __restrict__ taps_w, int taps,
+                  const int* __restrict__ token_seq, const int* __restrict__ cu_tokens, const int* __restrict__ state_slots,
+                  const float* __restrict__ state, long state_stride, long conv_offset, int num_slots,
+                  float* __restrict__ y, int Gq, int H, int dim, int vdim, int* err) {
+  __shared__ float red[32];
+  pdl_wait();
+  const int t = blockIdx.y, seg = blockIdx.x;
+  const int C = 2 * Gq * dim + H * vdim;
+  const bool unit = seg < 2 * Gq;
+  const int width = unit ? dim : vdim;
+  const int c0 = unit ? seg * dim : 2 * Gq * dim + (seg - 2 * Gq) * vdim;
+  const int s = token_seq[t];
+  const int p = t - cu_tokens[s];                     // index of the token among the request's tokens of this step
+  int slot = state_slots[s];
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0 && seg == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t, slot, num_slots);
+    slot = -1;
+  }
+  const float* old = slot >= 0 ? state + (size_t)slot * state_stride + conv_offset : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const int c = c0 + i;
+    float a = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;                  // tap j weighs the token `back` places before this one
+      float xv;
+      if (back <= p) xv = to_f32(x[(size_t)(t - back) * x_stride + c]);
+      else xv = old ? old[(size_t)(taps - 1 - (back - p)) * C + c] : 0.f;
+      a = fmaf(taps_w[(size_t)c * taps + j], xv, a);
+    }
+    a = a / (1.0f + expf(-a));
+    y[(size_t)t * C + c] = a;
+    ss += a * a;
+  }
+  if (!unit) return;
+  ss = block_sum(ss, red);
+  const float inv = (seg < Gq ? rsqrtf((float)dim) : 1.0f) / sqrtf(ss + 1e-6f);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) y[(size_t)t * C + c0 + i] *= inv;
+}
+
+// The last taps - 1 projected rows of every request, after this step: thread per (request, channel).
+template <typename TI>
+__global__ void delta_conv_state_kernel(const TI* __restrict__ x, long x_stride, int taps, const int* __restrict__ cu_tokens,
+                                        const int* __restrict__ state_slots, float* __restrict__ state, long state_stride,
+                                        long conv_offset, int num_slots, int C) {
+  pdl_wait();
+  const int s = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = state_slots[s];
+  if (c >= C || slot < 0 || slot >= num_slots) return;
+  const int t0 = cu_tokens[s], n = cu_tokens[s + 1] - t0;
+  if (n <= 0) return;
+  float* cs = state + (size_t)slot * state_stride + conv_offset;
+  const int keep = taps - 1;
+  // new row r (oldest first) is place n - keep + r of the step when that is >= 0, else old row r + n
+  for (int r = 0; r < keep; ++r) {               // ascending r reads old rows r + n > r: nothing read after it is overwritten
+    const int at = n - keep + r;
+    cs[(size_t)r * C + c] = at >= 0 ? to_f32(x[(size_t)(t0 + at) * x_stride + c]) : cs[(size_t)(r + n) * C + c];
+  }
+}
+
+// ---------------------------------------------------------------- the recurrence
+// One block per (request, head).  Thread j * RP + r holds rows r * RPT .. of value column j; the RP partial sums of a
+// column lie in neighbouring lanes and meet by shuffles.  The inputs of CH tokens are staged in shared memory (the next
+// chunk's are fetched into registers while the current one is computed), so the walk meets one barrier per chunk.
+#define DELTA_CH 8
+
+// The widest block a row count allows: a thread with many rows of state needs many registers.
+constexpr int delta_max_threads(int rpt) { return rpt >= 64 ? 256 : (rpt >= 32 ? 512 : 1024); }
+static inline int delta_tok_floats(int dimp, int vdim) { return 2 * dimp + ((vdim + 2 + 3) & ~3); }   // rows stay 16-byte aligned
+
+template <int RPT, int RP>
+__global__ void __launch_bounds__(delta_max_threads(RPT))
+delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_stride, int ab_dtype_bf16,
+                       const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                       const int* __restrict__ cu_tokens, const int* __restrict__ state_slots, float* __restrict__ state,
+                       long state_stride, int num_slots, float* __restrict__ o_out, int Gq, int H, int dim, int vdim, int* err) {
+  extern __shared__ __align__(16) float sm[];
+  pdl_wait();
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int t0 = cu_tokens[s], t1 = cu_tokens[s + 1];
+  if (t1 <= t0) return;
+  const int slot = state_slots[s];
+  if (slot >= num_slots) {
+    if (tid == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t0, slot, num_slots);
+    return;
+  }
+  const int C = 2 * Gq * dim + H * vdim;
+  const int dimp = RPT * RP;                              // rows padded to whole groups; the padding stays zero
+  const int j = tid / RP, r = tid % RP;
+  const bool active = j < vdim;
+  const int hq = h / (H / Gq);
+  const int row0 = r * RPT;
+  float* S = slot >= 0 ? state + (size_t)slot * state_stride + (size_t)h * dim * vdim : nullptr;
+  float st[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) st[i] = (S != nullptr && active && row0 + i < dim) ? S[(size_t)(row0 + i) * vdim + j] : 0.f;
+  // a chunk in shared memory: q [CH][dimp], k [CH][dimp], v [CH][vdim], g [CH], beta [CH]; two buffers
+  const int per_tok = 2 * dimp + ((vdim + 2 + 3) & ~3);
+  const int buf_floats = DELTA_CH * per_tok;
+  for (int i = tid; i < 2 * buf_floats; i += nthreads) sm[i] = 0.f;
+  const float decay_rate = expf(a_log[h]), bias = dt_bias[h];
+  const int per_chunk = DELTA_CH * (2 * dim + vdim + 2);  // values a chunk brings
+  constexpr int MAXV = 8;                                 // values a thread fetches per chunk (checked by the launcher)
+  float pre[MAXV];
+  auto fetch = [&](int c0) {
+#pragma unroll
+    for (int n = 0; n < MAXV; ++n) {
+      const int e = tid + n * nthreads;
+      float v = 0.f;
+      if (e < per_chunk) {
+        const int tt = e / (2 * dim + vdim + 2), w = e - tt * (2 * dim + vdim + 2);
+        const int t = c0 + tt;
+        if (t < t1) {
+          const float* row = y + (size_t)t * C;
+          if (w < dim) v = row[hq * dim + w];
+          else if (w < 2 * dim) v = row[(Gq + hq) * dim + (w - dim)];
+          else if (w < 2 * dim + vdim) v = row[2 * Gq * dim + h * vdim + (w - 2 * dim)];
+          else {
+            // the two per-head numbers of the token: raw decay input, then raw beta input
+            const int which = w - 2 * dim - vdim;
+            const size_t at = (size_t)t * ab_stride + (which == 0 ? h : H + h);
+            const float raw = ab_dtype_bf16 ? __bfloat162float(((const bf16*)x_ab)[at]) : x_ab[at];
+            if (which == 0) {
+              const float z = raw + bias;
+              const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));       // softplus
+              v = expf(-decay_rate * sp);
+            } else {
+              v = 1.0f / (1.0f + expf(-raw));
+            }
+          }
+        }
+      }
+      pre[n] = v;
+    }
+  };
+  auto stash = [&](int buf) {
+    float* b = sm + buf * buf_floats;
+#pragma unroll
+    for (int n = 0; n < MAXV; ++n) {
+      const int e = tid + n * nthreads;
+      if (e < per_chunk) {
+        const int tt = e / (2 * dim + vdim + 2), w = e - tt * (2 * dim + vdim + 2);
+        float* tok = b + tt * per_tok;
+        if (w < dim) tok[w] = pre[n];
+        else if (w < 2 * dim) tok[dimp + (w - dim)] = pre[n];
+        else tok[2 * dimp + (w - 2 * dim)] = pre[n];
+      }
+    }
+  };
+  __syncthreads();
+  fetch(t0);
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += DELTA_CH, buf ^= 1) {
+    stash(buf);
+    __syncthreads();
+    if (c0 + DELTA_CH < t1) fetch(c0 + DELTA_CH);
+    const float* b = sm + buf * buf_floats;
+    const int n = min(DELTA_CH, t1 - c0);
+    for (int tt = 0; tt < n; ++tt) {
+      const float* tok = b + tt * per_tok;
+      const float4* q4 = reinterpret_cast<const float4*>(tok + row0);
+      const float4* k4 = reinterpret_cast<const float4*>(tok + dimp + row0);
+      const float vj = active ? tok[2 * dimp + j] : 0.f;
+      const float g = tok[2 * dimp + vdim], beta = tok[2 * dimp + vdim + 1];
+      float p1 = 0.f, p2 = 0.f, kq = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 kk = k4[i], qq = q4[i];
+        p1 = fmaf(st[4 * i], kk.x, p1);     p2 = fmaf(st[4 * i], qq.x, p2);     kq = fmaf(kk.x, qq.x, kq);
+        p1 = fmaf(st[4 * i + 1], kk.y, p1); p2 = fmaf(st[4 * i + 1], qq.y, p2); kq = fmaf(kk.y, qq.y, kq);
+        p1 = fmaf(st[4 * i + 2], kk.z, p1); p2 = fmaf(st[4 * i + 2], qq.z, p2); kq = fmaf(kk.z, qq.z, kq);
+        p1 = fmaf(st[4 * i + 3], kk.w, p1); p2 = fmaf(st[4 * i + 3], qq.w, p2); kq = fmaf(kk.w, qq.w, kq);
+      }
+#pragma unroll
+      for (int o = RP / 2; o > 0; o >>= 1) {
+        p1 += __shfl_xor_sync(0xffffffffu, p1, o);
+        p2 += __shfl_xor_sync(0xffffffffu, p2, o);
+        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      }
+      const float u = beta * (vj - g * p1);
+#pragma unroll
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 kk = k4[i];
+        st[4 * i] = fmaf(g, st[4 * i], kk.x * u);
+        st[4 * i + 1] = fmaf(g, st[4 * i + 1], kk.y * u);
+        st[4 * i + 2] = fmaf(g, st[4 * i + 2], kk.z * u);
+        st[4 * i + 3] = fmaf(g, st[4 * i + 3], kk.w * u);
+      }
+      if (active && r == 0) o_out[(size_t)(c0 + tt) * H * vdim + (size_t)h * vdim + j] = fmaf(g, p2, u * kq);
+    }
+  }
+  if (S != nullptr && active) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i)
+      if (row0 + i < dim) S[(size_t)(row0 + i) * vdim + j] = st[i];
+  }
+}
+
+// out = o / sqrt(mean(o^2) + eps) * norm_w * silu(z): one warp per (token, head).
+template <typename TZ, typename TO>
+__global__ void __launch_bounds__(128)
+delta_out_kernel(const float* __restrict__ o, const TZ* z, long z_stride, const float* __restrict__ norm_w, float eps,
+                 TO* __restrict__ out, long out_stride, int T, int H, int vdim) {
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * 4 + warp;
+  if (item >= (long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item - (long)t * H);
+  const float* row = o + ((size_t)t * H + h) * vdim;
+  float ss = 0.f;
+  for (int i = lane; i < vdim; i += 32) ss += row[i] * row[i];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+  for (int i = lane; i < vdim; i += 32) {
+    const float zz = to_f32(z[(size_t)t * z_stride + (size_t)h * vdim + i]);
+    out[(size_t)t * out_stride + (size_t)h * vdim + i] = from_f32<TO>(row[i] * inv * norm_w[i] * (zz / (1.0f + expf(-zz))));
+  }
+}
+
+// x [T][>= C] of x_dtype (row stride x_stride): the projected q, k, v side by side; taps_w float [C][taps];
+// state float [num_slots][state_stride], a request's convolution rows at conv_offset; y float [T][C]: q, k (unit
+// vectors, q scaled) and v after the convolution.  Then the state's rows are brought up to date.
+PHOTON_API int photon_delta_conv(const void* x, long x_stride, int x_dtype, const float* taps_w, int taps, const int* token_seq,
+                                 const int* cu_tokens, const int* state_slots, float* state, long state_stride,
+                                 long conv_offset, int num_slots, float* y, int T, int S, int Gq, int H, int dim, int vdim,
+                                 int* err, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (taps < 1 || Gq <= 0 || H <= 0 || H % Gq || dim <= 0 || vdim <= 0) return PHOTON_ERR_ARGUMENT;
+  if (T > 65535 || S > 65535) return PHOTON_ERR_UNSUPPORTED;
+  const int C = 2 * Gq * dim + H * vdim;
+  dim3 grid(2 * Gq + H, T);
+  int st;
+  if (x_dtype == PHOTON_F32)
+    st = launch_pdl(delta_conv_kernel<float>, grid, dim3(128), 0, stream, (const float*)x, x_stride, taps_w, taps, token_seq, cu_tokens,
+                    state_slots, (const float*)state, state_stride, conv_offset, num_slots, y, Gq, H, dim, vdim, err);
+  else if (x_dtype == PHOTON_BF16)
+    st = launch_pdl(delta_conv_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)x, x_stride, taps_w, taps, token_seq, cu_tokens,
+                    state_slots, (const float*)state, state_stride, conv_offset, num_slots, y, Gq, H, dim, vdim, err);
+  else
+    return PHOTON_ERR_ARGUMENT;
+  if (st != 0 || taps == 1) return st;
+  dim3 g2((C + 127) / 128, S);
+  if (x_dtype == PHOTON_F32)
+    return launch_pdl(delta_conv_state_kernel<float>, g2, dim3(128), 0, stream, (const float*)x, x_stride, taps, cu_tokens, state_slots,
+                      state, state_stride, conv_offset, num_slots, C);
+  return launch_pdl(delta_conv_state_kernel<bf16>, g2, dim3(128), 0, stream, (const bf16*)x, x_stride, taps, cu_tokens, state_slots,
+                    state, state_stride, conv_offset, num_slots, C);
+}
+
+template <int RPT, int RP>
+static int delta_recurrent_launch(const float* y, const void* ab, long ab_stride, int ab_bf16, const float* a_log,
+                                  const float* dt_bias, const int* cu_tokens, const int* state_slots, float* state,
+                                  long state_stride, int num_slots, float* o, int S, int Gq, int H, int dim, int vdim, int* err,
+                                  cudaStream_t stream) {
+  // enough threads for the columns, and for fetching a chunk's inputs with at most 8 values a thread
+  const int fetchers = (DELTA_CH * (2 * dim + vdim + 2) + 7) / 8;
+  const int threads = ((max(vdim * RP, fetchers) + 31) / 32) * 32;
+  const int dimp = RPT * RP;
+  const size_t smem = (size_t)2 * DELTA_CH * delta_tok_floats(dimp, vdim) * sizeof(float);
+  if (threads > delta_max_threads(RPT) || smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_recurrent_kernel<RPT, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch_pdl(delta_recurrent_kernel<RPT, RP>, dim3(S, H), dim3(threads), smem, stream, y, (const float*)ab, ab_stride, ab_bf16,
+                    a_log, dt_bias, cu_tokens, state_slots, state, state_stride, num_slots, o, Gq, H, dim, vdim, err);
+}
+
+// y float [T][C] from photon_delta_conv; ab [T][>= 2 H] of ab_dtype (row stride ab_stride): the raw decay inputs of the
+// H heads, then the raw beta inputs; a_log, dt_bias float [H]; state as above with S [H][dim][vdim] at its start;
+// o float [T][H * vdim]: the read-outs before the norm.
+PHOTON_API int photon_delta_recurrent(const float* y, const void* ab, long ab_stride, int ab_dtype, const float* a_log,
+                                      const float* dt_bias, const int* cu_tokens, const int* state_slots, float* state,
+                                      long state_stride, int num_slots, float* o, int S, int Gq, int H, int dim, int vdim,
+                                      int* err, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  if (Gq <= 0 || H <= 0 || H % Gq || dim <= 0 || vdim <= 0) return PHOTON_ERR_ARGUMENT;
+  if (ab_dtype != PHOTON_F32 && ab_dtype != PHOTON_BF16) return PHOTON_ERR_ARGUMENT;
+  if (S > 2147483647 / 2 || H > 65535) return PHOTON_ERR_UNSUPPORTED;
+  const int bf = ab_dtype == PHOTON_BF16;
+  // lanes per column (RP, a power of two up to 32) and rows per lane (RPT, a multiple of 4): the block stays within
+  // 1024 threads and a thread within 32 rows of state where the sizes allow it
+#define DELTA_TRY(RPT, RP) if (dim <= RPT * RP && vdim * RP <= delta_max_threads(RPT) && \
+                               (DELTA_CH * (2 * dim + vdim + 2) + 7) / 8 <= delta_max_threads(RPT)) \
+    return delta_recurrent_launch<RPT, RP>(y, ab, ab_stride, bf, a_log, dt_bias, cu_tokens, state_slots, state, state_stride, num_slots, \
+                                           o, S, Gq, H, dim, vdim, err, stream)
+  DELTA_TRY(4, 4); DELTA_TRY(8, 4); DELTA_TRY(8, 8); DELTA_TRY(16, 4); DELTA_TRY(16, 8); DELTA_TRY(32, 4); DELTA_TRY(32, 8);
+  DELTA_TRY(16, 16); DELTA_TRY(32, 2); DELTA_TRY(64, 4); DELTA_TRY(64, 2); DELTA_TRY(64, 1); DELTA_TRY(128, 1); DELTA_TRY(128, 2);
+  return PHOTON_ERR_UNSUPPORTED;
+}
+
+// o float [T][H * vdim]; z [T][H * vdim] of z_dtype (row stride z_stride); norm_w float [vdim]; out [T][H * vdim] of out_dtype.
+PHOTON_API int photon_delta_out(const float* o, const void* z, long z_stride, int z_dtype, const float* norm_w, float eps,
+                                void* out, long out_stride, int out_dtype, int T, int H, int vdim, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long items = (long)T * H;
+  dim3 grid((unsigned)((items + 3) / 4));
+#define DOUT_GO(TZ, TO) return launch_pdl(delta_out_kernel<TZ, TO>, grid, dim3(128), 0, stream, o, (const TZ*)z, z_stride, norm_w, eps, \
+                                          (TO*)out, out_stride, T, H, vdim)
+  if (z_dtype == PHOTON_F32 && out_dtype == PHOTON_F32) DOUT_GO(float, float);
+  if (z_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16) DOUT_GO(float, bf16);
+  if (z_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16) DOUT_GO(bf16, bf16);
+  return PHOTON_ERR_ARGUMENT;
+}

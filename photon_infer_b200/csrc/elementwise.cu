@@ -64,7 +64,8 @@ template <typename TD, typename TO, bool VEC, bool CENTER = false>
 __global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* residual,   // written by earlier kernels that
                                    const void* __restrict__ w, int w_bf16,    // may still run when this one starts: no
                                    TO* out, const int* rows, int H, float eps,   // read-only path for them
-                                   const void* __restrict__ b = nullptr, int b_bf16 = 0) {
+                                   const void* __restrict__ b = nullptr, int b_bf16 = 0,
+                                   const float* __restrict__ dscale = nullptr) {   // [H]: delta is multiplied by it first
   __shared__ float red[32];
   extern __shared__ __align__(16) float stash[];               // H floats: the summed row
   pdl_wait();
@@ -79,6 +80,12 @@ __global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* res
       Quad<float>::load(res + i, v);
       if (d) {
         Quad<TD>::load(d + i, dv);
+        if (dscale) {
+          float sc[4];
+          Quad<float>::load(dscale + i, sc);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dv[e] *= sc[e];
+        }
         if (d2) {
           float dw[4];
           Quad<TD>::load(d2 + i, dw);
@@ -95,7 +102,10 @@ __global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* res
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = res[i];
-      if (d) v += d2 ? to_f32(d[i]) + to_f32(d2[i]) : to_f32(d[i]);
+      if (d) {
+        const float d1 = dscale ? to_f32(d[i]) * dscale[i] : to_f32(d[i]);
+        v += d2 ? d1 + to_f32(d2[i]) : d1;
+      }
       stash[i] = v;
       ss += v * v;
     }
@@ -136,11 +146,11 @@ __global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* res
 template <typename TD, typename TO, bool CENTER = false>
 static int add_rmsnorm_launch(const void* delta, const void* delta2, float* residual, const void* w, int w_bf16, void* out,
                               const int* rows, int n, int H, float eps, cudaStream_t stream,
-                              const void* b = nullptr, int b_bf16 = 0) {
+                              const void* b = nullptr, int b_bf16 = 0, const float* dscale = nullptr) {
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   const bool vec = (H % 4 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)delta2 % 16 == 0) && ((uintptr_t)residual % 16 == 0) &&
-                   ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
+                   ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)dscale % 16 == 0);
   if (smem > 48 * 1024) {
     cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true, CENTER>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -152,51 +162,66 @@ static int add_rmsnorm_launch(const void* delta, const void* delta2, float* resi
   while (threads < 1024 && threads * 4 < H) threads <<= 1;   // depends on H only
   if (vec)
     return launch_pdl(add_rmsnorm_kernel<TD, TO, true, CENTER>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
-                      (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps, b, b_bf16);
+                      (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps, b, b_bf16, dscale);
   return launch_pdl(add_rmsnorm_kernel<TD, TO, false, CENTER>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
-                    (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps, b, b_bf16);
+                    (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps, b, b_bf16, dscale);
 }
 
 // delta may be null (plain norm); delta2 (same type as delta, may be null) is added as well: the sum of the two is
 // formed first, in 32-bit, and then added to the residual.  delta_dtype / out_dtype: PHOTON_F32 or PHOTON_BF16.
-PHOTON_API int photon_add_rmsnorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+// delta_scale (float [H], may be null): delta is multiplied by it, channel by channel, before the sums.
+PHOTON_API int photon_add_rmsnorm_scaled(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
                                   int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
-                                  float eps, cudaStream_t stream) {
+                                  float eps, const float* delta_scale, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int wb = (w_dtype == PHOTON_BF16);
   if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16)
-    return add_rmsnorm_launch<bf16, bf16>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<bf16, bf16>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, nullptr, 0, delta_scale);
   if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_F32)
-    return add_rmsnorm_launch<float, float>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<float, float>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, nullptr, 0, delta_scale);
   if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16)
-    return add_rmsnorm_launch<float, bf16>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<float, bf16>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, nullptr, 0, delta_scale);
   if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_F32)
-    return add_rmsnorm_launch<bf16, float>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<bf16, float>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, nullptr, 0, delta_scale);
   return PHOTON_ERR_ARGUMENT;
+}
+
+PHOTON_API int photon_add_rmsnorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+                                  int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
+                                  float eps, cudaStream_t stream) {
+  return photon_add_rmsnorm_scaled(delta, delta_dtype, delta2, residual, w, w_dtype, out, out_dtype, rows, n, H, eps, nullptr, stream);
 }
 
 // The same with a layer norm: out = (x - mean(x)) / sqrt(var(x) + eps) * w + b, x = residual + delta (+ delta2).
 // b may be null.
-PHOTON_API int photon_add_layernorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+PHOTON_API int photon_add_layernorm_scaled(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
                                     int w_dtype, const void* b, int b_dtype, void* out, int out_dtype, const int* rows,
-                                    int n, int H, float eps, cudaStream_t stream) {
+                                    int n, int H, float eps, const float* delta_scale, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int wb = (w_dtype == PHOTON_BF16), bb = (b_dtype == PHOTON_BF16);
   if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16)
-    return add_rmsnorm_launch<bf16, bf16, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+    return add_rmsnorm_launch<bf16, bf16, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb, delta_scale);
   if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_F32)
-    return add_rmsnorm_launch<float, float, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+    return add_rmsnorm_launch<float, float, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb, delta_scale);
   if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16)
-    return add_rmsnorm_launch<float, bf16, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+    return add_rmsnorm_launch<float, bf16, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb, delta_scale);
   if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_F32)
-    return add_rmsnorm_launch<bf16, float, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+    return add_rmsnorm_launch<bf16, float, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb, delta_scale);
   return PHOTON_ERR_ARGUMENT;
+}
+
+PHOTON_API int photon_add_layernorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+                                    int w_dtype, const void* b, int b_dtype, void* out, int out_dtype, const int* rows,
+                                    int n, int H, float eps, cudaStream_t stream) {
+  return photon_add_layernorm_scaled(delta, delta_dtype, delta2, residual, w, w_dtype, b, b_dtype, out, out_dtype, rows, n, H, eps,
+                                     nullptr, stream);
 }
 
 // ---------------------------------------------------------------- gated activation (SwiGLU, GeGLU)
 // gate_up [T, 2*I]: columns [0, I) are the gate, [I, 2I) the up projection.  out [T, I] = act(gate) * up.
 // act 0: silu, g / (1 + exp(-g)); act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
 __device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == PHOTON_ACT_RELU) return fmaxf(g, 0.f);
   if (act == PHOTON_ACT_GELU) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
   if (act == PHOTON_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return g / (1.0f + expf(-g));
@@ -241,7 +266,7 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__
 }
 
 PHOTON_API int photon_glu(const void* gate_up, void* out, int dtype, int T, int I, int act, cudaStream_t stream) {
-  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH && act != PHOTON_ACT_GELU) return PHOTON_ERR_ARGUMENT;
+  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH && act != PHOTON_ACT_GELU && act != PHOTON_ACT_RELU) return PHOTON_ERR_ARGUMENT;
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int threads = 256;
@@ -345,7 +370,7 @@ __global__ void activation_vec_kernel(const T* x, T* out, size_t total_vecs, int
 }
 
 PHOTON_API int photon_activation(const void* x, void* out, int dtype, long total, int act, cudaStream_t stream) {
-  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH && act != PHOTON_ACT_GELU) return PHOTON_ERR_ARGUMENT;
+  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH && act != PHOTON_ACT_GELU && act != PHOTON_ACT_RELU) return PHOTON_ERR_ARGUMENT;
   if (total <= 0) return 0;
   const int n = dtype == PHOTON_BF16 ? 8 : 4;
   const bool vec = (total % n == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0);

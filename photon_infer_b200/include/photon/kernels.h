@@ -53,6 +53,7 @@ extern "C" {
 #define PHOTON_ACT_SILU 0
 #define PHOTON_ACT_GELU_TANH 1
 #define PHOTON_ACT_GELU 2            /* the exact form, 0.5 z (1 + erf(z / sqrt 2)) */
+#define PHOTON_ACT_RELU 3
 #define PHOTON_ACT_NONE (-1)
 
 /* ------------------------------------------------------------------ elementwise.cu */
@@ -64,6 +65,13 @@ PHOTON_EXPORT int photon_embedding(const int* ids, const void* table, int table_
  * rows (may be null): only these rows are read, nothing is written back, out has one row per entry. */
 PHOTON_EXPORT int photon_add_rmsnorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
                        int w_dtype, void* out, int out_dtype, const int* rows, int n, int H, float eps, cudaStream_t stream);
+/* The same with delta multiplied channel by channel by delta_scale (float [H], may be null) before the sums. */
+PHOTON_EXPORT int photon_add_rmsnorm_scaled(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+                       int w_dtype, void* out, int out_dtype, const int* rows, int n, int H, float eps,
+                       const float* delta_scale, cudaStream_t stream);
+PHOTON_EXPORT int photon_add_layernorm_scaled(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+                         int w_dtype, const void* b, int b_dtype, void* out, int out_dtype, const int* rows, int n, int H,
+                         float eps, const float* delta_scale, cudaStream_t stream);
 /* The same with a layer norm: out = (x - mean(x)) / sqrt(var(x) + eps) * w + b, x = residual + delta (+ delta2); b may be null. */
 PHOTON_EXPORT int photon_add_layernorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
                          int w_dtype, const void* b, int b_dtype, void* out, int out_dtype, const int* rows, int n, int H,
@@ -159,6 +167,44 @@ PHOTON_EXPORT int photon_latent_decode_attention(const void* q, long q_stride, c
                                    int max_pages, const int* token_seq, const int* positions, int T_, int heads, int width,
                                    int dv, int page_size, int num_pages, float scale, int splits, float* part, void* out,
                                    long out_stride, int* err, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ delta.cu: gated delta rule (recurrent state, short convolutions) */
+/* The state row of a request: S float [H][dim][vdim], then at conv_offset the last taps - 1 projected rows [taps - 1][C],
+ * C = 2 Gq dim + H vdim (Gq query/key heads, H value heads); a state slot of -1 starts from zeros and stores nothing.
+ * photon_delta_conv: x [T][>= C] of x_dtype (q, k, v projected, side by side); y float [T][C] = silu(causal convolution per
+ * channel, taps_w float [C][taps], last column the current token), q and k heads made unit vectors, q times dim^(-1/2);
+ * then the state's rows are brought up to date. */
+PHOTON_EXPORT int photon_delta_conv(const void* x, long x_stride, int x_dtype, const float* taps_w, int taps, const int* token_seq,
+                      const int* cu_tokens, const int* state_slots, float* state, long state_stride, long conv_offset,
+                      int num_slots, float* y, int T, int S, int Gq, int H, int dim, int vdim, int* err, cudaStream_t stream);
+/* Per (request, head): g = exp(-exp(a_log) softplus(a + dt_bias)), beta = sigmoid(b); S <- g S; u = beta (v - S^T k);
+ * S <- S + k u^T; o = S^T q.  ab [T][>= 2 H] of ab_dtype: the a of the H heads, then the b; o float [T][H * vdim]. */
+PHOTON_EXPORT int photon_delta_recurrent(const float* y, const void* ab, long ab_stride, int ab_dtype, const float* a_log,
+                           const float* dt_bias, const int* cu_tokens, const int* state_slots, float* state,
+                           long state_stride, int num_slots, float* o, int S, int Gq, int H, int dim, int vdim, int* err,
+                           cudaStream_t stream);
+/* out = o / sqrt(mean(o^2) + eps) * norm_w * silu(z) per head over vdim; z [T][H * vdim] of z_dtype, norm_w float [vdim]. */
+PHOTON_EXPORT int photon_delta_out(const float* o, const void* z, long z_stride, int z_dtype, const float* norm_w, float eps,
+                     void* out, long out_stride, int out_dtype, int T, int H, int vdim, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ attention_talk.cu: attention whose heads' scores are mixed */
+/* Bias (float, may be null) on q [T][H * d] and k [T][G * d] of in_dtype, rotation of the first rot_dims numbers of a head
+ * (number j with j + rot_dims / 2, angle positions[t] * inv_freq[j]); q_out of out_dtype; the rotated key goes to k_cache, the
+ * value to v_cache (may be null): v [T][G * d] or, with v null, the key before its rotation; both caches
+ * [pages][G][page_size][d], written at slot_mapping[t] (-1: nothing). */
+PHOTON_EXPORT int photon_talk_prep(const void* q, long q_stride, const void* k, long k_stride, const void* v, long v_stride,
+                     int in_dtype, const float* q_bias,
+                     const float* k_bias, void* q_out, long qo_stride, int out_dtype, const int* positions,
+                     const double* inv_freq, int rot_dims, const int* slot_mapping, void* k_cache, void* v_cache, int T, int H,
+                     int G, int d, int page_size, long num_slots, int* err, cudaStream_t stream);
+/* raw_g = (q_g . k) qmul[g]; s_h = sum_g talk[h][g] raw_g; softmax over the keys max(0, p - window + 1) .. p with exp(sink[h])
+ * in the denominator; out_h = sigmoid(gate_h) sum_j p_h(j) v(j).  talk [H][H], sink [H], gate (float rows of H, stride
+ * gate_stride) may be null; window 0: none; splits > 1: part float [T * splits * H * (d + 2)]. */
+PHOTON_EXPORT int photon_talk_attention(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                          const void* v_cache, int dtype, const int* block_table, int max_pages, const int* token_seq,
+                          const int* positions, int T, int H, int G, int d, int page_size, int num_pages, int window,
+                          const float* qmul, const float* talk, const float* sink, const float* gate, long gate_stride,
+                          int splits, float* part, int* err, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ gla.cu: gated linear attention (recurrent state) */
 /* Per (request, head): S = diag(a_t) S + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau), z_t = w_a2 low_t + b_a2, o_t = S^T (q_t *

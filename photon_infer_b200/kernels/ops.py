@@ -107,12 +107,15 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Op
 
 
 def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None) -> None:
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None,
+                delta_scale: Optional[torch.Tensor] = None) -> None:
     """``residual += delta`` in float32 (in place; skipped when ``rows`` is given), then
     ``out = weight * (residual / sqrt(mean(residual^2) + eps))``.  With ``rows`` (int32 list)
     only those rows are read and ``out`` has one row per list entry.  ``delta2`` (the second output of a
-    parallel block, same shape and type as ``delta``): ``residual += delta + delta2``."""
-    _cuda(delta, residual, weight, out, rows, delta2)
+    parallel block, same shape and type as ``delta``): ``residual += delta + delta2``.  ``delta_scale`` (float32
+    ``[H]``): ``delta`` is multiplied by it channel by channel first (a layer scale)."""
+    _cuda(delta, residual, weight, out, rows, delta2, delta_scale)
+    _check_delta_scale(delta_scale, delta, delta2, residual.shape[-1])
     if delta2 is not None:
         if delta is None:
             delta, delta2 = delta2, None
@@ -128,23 +131,34 @@ def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: t
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_rmsnorm: out must be [rows, H] and weight [H]")
     if rows is not None:
         _int32(rows, "rows")
-    f = _fn("elementwise", "photon_add_rmsnorm",
-            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    f = _fn("elementwise", "photon_add_rmsnorm_scaled",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
+             c_void_p])
     _check(f(_ptr(delta), _dtype_code(delta) if delta is not None else F32, _ptr(delta2), _ptr(residual), _ptr(weight),
-             _dtype_code(weight), _ptr(out), _dtype_code(out), _ptr(rows), n, H, float(eps), _stream()),
+             _dtype_code(weight), _ptr(out), _dtype_code(out), _ptr(rows), n, H, float(eps), _ptr(delta_scale), _stream()),
            "add_rmsnorm")
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}     # gelu: the exact (erf) form
+def _check_delta_scale(scale: Optional[torch.Tensor], delta, delta2, H: int) -> None:
+    if scale is None:
+        return
+    if delta is None or delta2 is not None:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "a channel scale goes with exactly one pending output")
+    if scale.dtype != torch.float32 or scale.numel() != H or not scale.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "the channel scale must be contiguous float32 [H]")
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu": 2, "relu": 3}     # gelu: the exact (erf) form
 ACT_NONE = -1
 
 
 def add_layernorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                   eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
-                  delta2: Optional[torch.Tensor] = None) -> None:
+                  delta2: Optional[torch.Tensor] = None, delta_scale: Optional[torch.Tensor] = None) -> None:
     """As ``add_rmsnorm`` with a layer norm: ``out = (x - mean(x)) / sqrt(var(x) + eps) * weight + bias`` with
     ``x = residual + delta (+ delta2)``, all in 32-bit; the variance is the mean of the squared deviations."""
-    _cuda(delta, residual, weight, bias, out, rows, delta2)
+    _cuda(delta, residual, weight, bias, out, rows, delta2, delta_scale)
+    _check_delta_scale(delta_scale, delta, delta2, residual.shape[-1])
     if delta2 is not None:
         if delta is None:
             delta, delta2 = delta2, None
@@ -160,12 +174,12 @@ def add_layernorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight:
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_layernorm: out must be [rows, H], weight and bias [H]")
     if rows is not None:
         _int32(rows, "rows")
-    f = _fn("elementwise", "photon_add_layernorm",
+    f = _fn("elementwise", "photon_add_layernorm_scaled",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
-             c_float, c_void_p])
+             c_float, c_void_p, c_void_p])
     _check(f(_ptr(delta), _dtype_code(delta) if delta is not None else F32, _ptr(delta2), _ptr(residual), _ptr(weight),
              _dtype_code(weight), _ptr(bias), _dtype_code(bias) if bias is not None else F32, _ptr(out), _dtype_code(out),
-             _ptr(rows), n, H, float(eps), _stream()), "add_layernorm")
+             _ptr(rows), n, H, float(eps), _ptr(delta_scale), _stream()), "add_layernorm")
 
 
 def activation(x: torch.Tensor, activation: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -1115,6 +1129,163 @@ def causal_softmax_rows(scores: torch.Tensor, probs: torch.Tensor, heads: int, f
             [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(scores), scores.stride(0), _ptr(probs), probs.stride(0), _dtype_code(probs), rows, int(heads), int(first_pos),
              cols, float(scale), _stream()), "causal_softmax_rows")
+
+
+# ----------------------------------------------------------------------------- gated delta rule
+
+def delta_conv(x: torch.Tensor, taps_w: torch.Tensor, token_seq: torch.Tensor, cu_tokens: torch.Tensor,
+               state_slots: torch.Tensor, state: torch.Tensor, conv_offset: int, y: torch.Tensor, num_seqs: int, qk_heads: int,
+               heads: int, dim: int, vdim: int, err: Optional[torch.Tensor]) -> None:
+    """Short causal convolution with silu over the projected ``[q | k | v]`` rows ``x [T, C]`` (a view with a row
+    stride), ``taps_w [C, taps]`` float32; q and k heads become unit vectors (q also times ``dim^-0.5``); ``y [T, C]``
+    float32.  The ``taps - 1`` rows before a request's first token of the step come from its state row (at
+    ``conv_offset``), which is then brought up to date.  ``state [slots, row]`` float32."""
+    _cuda(x, taps_w, token_seq, cu_tokens, state_slots, state, y, err)
+    T = x.shape[0]
+    C = 2 * qk_heads * dim + heads * vdim
+    taps = taps_w.shape[1]
+    if x.shape[1] != C or x.stride(1) != 1 or taps_w.shape != (C, taps) or taps_w.dtype != torch.float32 or not taps_w.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"delta_conv: x [T, {C}] and float32 taps [{C}, taps]")
+    if y.shape != (T, C) or y.dtype != torch.float32 or not y.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "delta_conv: y must be contiguous float32 [T, C]")
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < conv_offset + (taps - 1) * C:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "delta_conv: state must be contiguous float32 [slots, row] with room for the taps")
+    for t, what in ((token_seq, "token_seq"), (cu_tokens, "cu_tokens"), (state_slots, "state_slots")):
+        _int32(t, what)
+    f = _fn("delta", "photon_delta_conv",
+            [c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _dtype_code(x), _ptr(taps_w), taps, _ptr(token_seq), _ptr(cu_tokens), _ptr(state_slots),
+             _ptr(state), state.stride(0), int(conv_offset), state.shape[0], _ptr(y), T, int(num_seqs), qk_heads, heads, dim, vdim,
+             _ptr(err), _stream()), "delta_conv")
+
+
+def delta_recurrent(y: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, cu_tokens: torch.Tensor,
+                    state_slots: torch.Tensor, state: torch.Tensor, o: torch.Tensor, num_seqs: int, qk_heads: int, heads: int,
+                    dim: int, vdim: int, err: Optional[torch.Tensor]) -> None:
+    """The gated delta rule over the tokens of a step, request by request: ``y [T, C]`` from ``delta_conv``,
+    ``ab [T, 2 heads]`` (a view with a row stride: the raw decay inputs, then the raw beta inputs), ``a_log``,
+    ``dt_bias`` float32 ``[heads]``; ``o [T, heads * vdim]`` float32 receives the read-outs.  The state matrices are
+    the first ``heads * dim * vdim`` numbers of a request's state row."""
+    _cuda(y, ab, a_log, dt_bias, cu_tokens, state_slots, state, o, err)
+    T = y.shape[0]
+    if ab.shape != (T, 2 * heads) or ab.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "delta_recurrent: ab must be [T, 2 * heads]")
+    if o.shape != (T, heads * vdim) or o.dtype != torch.float32 or not o.is_contiguous() or y.dtype != torch.float32 or not y.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "delta_recurrent: y and o must be contiguous float32")
+    for t in (a_log, dt_bias):
+        if t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "delta_recurrent: a_log and dt_bias float32 [heads]")
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < heads * dim * vdim:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "delta_recurrent: state must be contiguous float32 [slots, row]")
+    _int32(cu_tokens, "cu_tokens")
+    _int32(state_slots, "state_slots")
+    f = _fn("delta", "photon_delta_recurrent",
+            [c_void_p, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(y), _ptr(ab), ab.stride(0), _dtype_code(ab), _ptr(a_log), _ptr(dt_bias), _ptr(cu_tokens), _ptr(state_slots),
+             _ptr(state), state.stride(0), state.shape[0], _ptr(o), int(num_seqs), qk_heads, heads, dim, vdim, _ptr(err),
+             _stream()), "delta_recurrent")
+
+
+def delta_out(o: torch.Tensor, z: torch.Tensor, norm_w: torch.Tensor, eps: float, out: torch.Tensor, heads: int, vdim: int) -> None:
+    """``out = o / sqrt(mean(o^2) + eps) * norm_w * silu(z)`` per head over ``vdim``; ``o`` float32, ``z`` a view."""
+    _cuda(o, z, norm_w, out)
+    T = o.shape[0]
+    if z.shape != o.shape or z.stride(1) != 1 or out.shape != o.shape or out.stride(1) != 1 or norm_w.dtype != torch.float32 \
+            or norm_w.numel() != vdim or o.dtype != torch.float32 or not o.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "delta_out: o float32 [T, heads * vdim], z and out alike, norm_w float32 [vdim]")
+    f = _fn("delta", "photon_delta_out", [c_void_p, c_void_p, c_long, c_int, c_void_p, c_float, c_void_p, c_long, c_int, c_int,
+                                          c_int, c_int, c_void_p])
+    _check(f(_ptr(o), _ptr(z), z.stride(0), _dtype_code(z), _ptr(norm_w), float(eps), _ptr(out), out.stride(0), _dtype_code(out),
+             T, heads, vdim, _stream()), "delta_out")
+
+
+# ----------------------------------------------------------------------------- attention whose heads' scores are mixed
+
+def talk_prep(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor],
+              q_out: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int,
+              slot_mapping: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+              n_q: int, n_kv: int, d: int, err: Optional[torch.Tensor]) -> None:
+    """Bias and rotation of the projected ``q [T, n_q * d]`` and ``k [T, n_kv * d]`` (views with row strides) in
+    32-bit; ``q_out`` gets the queries, ``k_cache`` the rotated keys and ``v_cache`` (may be None) the values:
+    ``v [T, n_kv * d]`` or, with ``v`` None, the keys before their rotation; all at ``slot_mapping``.  ``k_cache``
+    None: nothing is stored."""
+    _cuda(q, k, v, q_bias, k_bias, q_out, positions, inv_freq, slot_mapping, k_cache, v_cache, err)
+    T = q.shape[0]
+    if q.shape != (T, n_q * d) or q.stride(1) != 1 or q_out.shape != (T, n_q * d) or q_out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_prep: q and q_out must be [T, n_q * d]")
+    store = k_cache is not None
+    if v is not None and (v.shape != (T, n_kv * d) or v.stride(1) != 1 or v.dtype != q.dtype or v_cache is None):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_prep: v must be [T, n_kv * d] of q's type, with a value cache")
+    if store and (k is None or k.shape != (T, n_kv * d) or k.stride(1) != 1 or k.dtype != q.dtype or slot_mapping is None
+                  or k_cache.dim() != 4 or k_cache.shape[1] != n_kv or k_cache.shape[3] != d or not k_cache.is_contiguous()
+                  or k_cache.dtype != q_out.dtype or (v_cache is not None and (v_cache.shape != k_cache.shape or not v_cache.is_contiguous()
+                                                                                  or v_cache.dtype != k_cache.dtype))):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_prep: k [T, n_kv * d] and caches [pages, n_kv, page, d] of q_out's type")
+    for b, n in ((q_bias, n_q * d), (k_bias, n_kv * d)):
+        if b is not None and (b.dtype != torch.float32 or b.numel() != n or not b.is_contiguous()):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_prep: biases must be contiguous float32")
+    if inv_freq is not None and (inv_freq.dtype != torch.float64 or inv_freq.numel() != rot_dims // 2):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_prep: inv_freq must be float64 [rot_dims / 2]")
+    _int32(positions, "positions")
+    page_size = k_cache.shape[2] if store else 1
+    num_slots = k_cache.shape[0] * page_size if store else 0
+    f = _fn("attention_talk", "photon_talk_prep",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p,
+             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_long, c_void_p, c_void_p])
+    v_in = v if store and v is not None else None
+    _check(f(_ptr(q), q.stride(0), _ptr(k if store else None), k.stride(0) if store else 0, _ptr(v_in),
+             v_in.stride(0) if v_in is not None else 0, _dtype_code(q), _ptr(q_bias),
+             _ptr(k_bias), _ptr(q_out), q_out.stride(0), _dtype_code(q_out), _ptr(positions), _ptr(inv_freq),
+             int(rot_dims) if inv_freq is not None else 0, _ptr(slot_mapping if store else None), _ptr(k_cache if store else None),
+             _ptr(v_cache if store else None), T, n_q, n_kv, d, page_size, num_slots, _ptr(err), _stream()), "talk_prep")
+
+
+_talk_scratch = {}
+
+
+def talk_scratch(device, floats: int) -> torch.Tensor:
+    """Partial results of split attention: one buffer per device that only grows; a buffer it outgrows is kept,
+    because a captured step may hold its address."""
+    key = (device.type, device.index)
+    kept = _talk_scratch.setdefault(key, [])
+    if not kept or kept[-1].numel() < floats:
+        kept.append(torch.empty((max(floats, 1 << 20),), dtype=torch.float32, device=device))
+    return kept[-1]
+
+
+def talk_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                   token_seq: torch.Tensor, positions: torch.Tensor, n_q: int, n_kv: int, d: int, window: Optional[int],
+                   qmul: torch.Tensor, talk: Optional[torch.Tensor], sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                   err: Optional[torch.Tensor], splits: int = 1) -> None:
+    """Paged causal attention over all heads of a token at once: raw scores times ``qmul [n_q]``, mixed across the heads
+    by ``talk [n_q, n_q]``, a window, ``exp(sink[h])`` in the softmax's denominator, outputs times ``sigmoid(gate)``
+    (``gate [T, n_q]`` float32, a view).  The general kernel: 32-bit arithmetic on any sizes, a sum's order depends on
+    the token's position alone (``splits`` 1)."""
+    _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, qmul, talk, sink, gate, err)
+    T = q.shape[0]
+    if q.shape != (T, n_q * d) or q.stride(1) != 1 or out.shape != (T, n_q * d) or out.stride(1) != 1 or out.dtype != q.dtype:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention: q and out must be [T, n_q * d] of one type")
+    if k_cache.dim() != 4 or k_cache.shape[1] != n_kv or k_cache.shape[3] != d or v_cache.shape != k_cache.shape \
+            or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention: caches must be [pages, n_kv, page, d] of q's type")
+    for t_, n in ((qmul, n_q), (talk, n_q * n_q), (sink, n_q)):
+        if t_ is not None and (t_.dtype != torch.float32 or t_.numel() != n or not t_.is_contiguous()):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention: qmul, talk and sink must be contiguous float32")
+    if gate is not None and (gate.shape != (T, n_q) or gate.dtype != torch.float32 or gate.stride(1) != 1):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention: gate must be float32 [T, n_q]")
+    for t_, what in ((block_table, "block_table"), (token_seq, "token_seq"), (positions, "positions")):
+        _int32(t_, what)
+    part = talk_scratch(q.device, T * splits * n_q * (d + 2)) if splits > 1 else None
+    f = _fn("attention_talk", "photon_talk_attention",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_void_p,
+             c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _dtype_code(q), _ptr(block_table),
+             block_table.shape[1], _ptr(token_seq), _ptr(positions), T, n_q, n_kv, d, k_cache.shape[2], k_cache.shape[0],
+             int(window or 0), _ptr(qmul), _ptr(talk), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+             int(splits), _ptr(part), _ptr(err), _stream()), "talk_attention")
 
 
 # ----------------------------------------------------------------------------- gated linear attention

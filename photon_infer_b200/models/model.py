@@ -36,8 +36,11 @@ def _build_layer(ls: LayerSpec, encodings: Dict[str, Part]) -> Block:
     mixer = create_part("mixer", ls.mixer.kind, mixer_params)
     norm2 = create_part("norm", ls.norm2.kind, ls.norm2.params) if ls.norm2 is not None else None
     ff = create_part("feed_forward", ls.feed_forward.kind, ls.feed_forward.params) if ls.feed_forward is not None else None
-    return create_part("block", ls.block.kind, dict(ls.block.params, norm1=norm1, mixer=mixer, norm2=norm2,
-                                                    feed_forward=ff))
+    params = dict(ls.block.params, norm1=norm1, mixer=mixer, norm2=norm2, feed_forward=ff)
+    for key, ps in (("scale1", ls.scale1), ("scale2", ls.scale2)):
+        if ps is not None:
+            params[key] = create_part("scale", ps.kind, ps.params)
+    return create_part("block", ls.block.kind, params)
 
 
 def _layer_part_prefixes(ls: LayerSpec) -> Dict[str, str]:
@@ -46,6 +49,9 @@ def _layer_part_prefixes(ls: LayerSpec) -> Dict[str, str]:
         out["norm2"] = ls.prefix + ls.norm2.prefix
     if ls.feed_forward is not None:
         out["feed_forward"] = ls.prefix + ls.feed_forward.prefix
+    for key, ps in (("scale1", ls.scale1), ("scale2", ls.scale2)):
+        if ps is not None:
+            out[key] = ls.prefix + ps.prefix
     return out
 
 
@@ -60,6 +66,8 @@ class _Skeleton:
         self.stream_parts: Dict[str, Part] = {name: create_part("stream", ps.kind, ps.params)
                                               for name, ps in spec.stream_parts.items()}
         self.final_norm = create_part("norm", spec.final_norm.kind, spec.final_norm.params)
+        self.embedding_norm = (create_part("norm", spec.embedding_norm.kind, spec.embedding_norm.params)
+                               if spec.embedding_norm is not None else None)
 
     def named_parts(self) -> List[Tuple[str, Part]]:
         out: List[Tuple[str, Part]] = []
@@ -72,6 +80,8 @@ class _Skeleton:
             for key, part in block.parts().items():
                 out.append((prefixes[key], part))
         out.append((self.spec.final_norm.prefix, self.final_norm))
+        if self.embedding_norm is not None:
+            out.append((self.spec.embedding_norm.prefix, self.embedding_norm))
         return out
 
     def declared(self) -> Dict[str, TensorSpec]:
@@ -103,6 +113,7 @@ class CausalLM:
         self.blocks = sk.blocks
         self.stream_parts = sk.stream_parts
         self.final_norm = sk.final_norm
+        self.embedding_norm = sk.embedding_norm
         self._skeleton = sk
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
@@ -161,6 +172,8 @@ class CausalLM:
         ops.embedding(ctx.token_ids, self.embedding, residual, ctx.error_flag)
         if self.spec.embedding_scale is not None:
             ops.scale_bias_rows(residual, self.spec.embedding_scale)
+        if self.embedding_norm is not None:
+            residual = self.embedding_norm.forward(residual, torch.float32)        # the normed rows are the stream
         # the embedding output is kept when a stream part will read it again (the blocks add into `residual` in place)
         first = residual.clone() if any(e.before is not None for e in self.spec.run) else None
         delta = None

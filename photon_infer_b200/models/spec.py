@@ -25,6 +25,10 @@ class LayerSpec:
     norm2: Optional[PartSpec]               # None: the arrangement has one norm
     feed_forward: Optional[PartSpec]        # None: a layer without a feed-forward
     prefix: str                             # e.g. "model.layers.3."
+    # optional learned vectors (kind "channel_scale") that multiply the mixer's and the feed-forward's output channel
+    # by channel before it is added to the residual stream
+    scale1: Optional[PartSpec] = None
+    scale2: Optional[PartSpec] = None
 
 
 @dataclasses.dataclass
@@ -59,6 +63,8 @@ class ModelSpec:
     # logits by ``logit_scale`` after the head (architectures that scale either; None: untouched)
     embedding_scale: Optional[float] = None
     logit_scale: Optional[float] = None
+    # a norm that the embedded rows pass before the first block (None: they enter the stream as they are)
+    embedding_norm: Optional[PartSpec] = None
     # parts that work on the residual stream between layers, by name (see RunEntry.before)
     stream_parts: Dict[str, PartSpec] = dataclasses.field(default_factory=dict)
 

@@ -162,11 +162,33 @@ class Part:
         return 0
 
 
+@dataclasses.dataclass
+class Scaled:
+    """A pending output whose channels are multiplied by a learned vector before the sum:
+    ``residual += scale * tensor`` (``scale [H]``, 32-bit); the norm that follows does both in its kernel."""
+    tensor: torch.Tensor
+    scale: torch.Tensor
+
+    def materialize(self) -> torch.Tensor:
+        """The scaled rows as a 32-bit tensor, for a consumer that cannot take the vector into its own kernel."""
+        return self.tensor.to(torch.float32) * self.scale.to(torch.float32)
+
+
+def delta_terms(delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """``(d1, d2, scale)``: what is pending on the stream as ``scale * d1 + d2`` (each may be None)."""
+    if isinstance(delta, Scaled):
+        return delta.tensor, None, delta.scale
+    d1, d2 = delta_pair(delta)
+    return d1, d2, None
+
+
 def delta_pair(delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
     """What a block hands on to be added to the residual stream: nothing, one tensor, or the two outputs of a
     parallel block (mixer and feed-forward), which are summed with each other first and then into the stream."""
     if delta is None:
         return None, None
+    if isinstance(delta, Scaled):
+        return delta.materialize(), None
     if isinstance(delta, (tuple, list)):
         parts = [d for d in delta if d is not None]
         if len(parts) > 2:
@@ -237,6 +259,14 @@ class FeedForward(Part):
     def forward_with_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], norm: Norm,
                           ctx: StepContext) -> Tuple[torch.Tensor, torch.Tensor]:
         raise NotImplementedError
+
+
+class ChannelScalePart(Part):
+    """A learned vector ``[H]`` that multiplies a sublayer's output channel by channel (``vector`` below, 32-bit)."""
+    vector: Optional[torch.Tensor] = None
+
+    def apply(self, x: torch.Tensor) -> "Scaled":
+        return Scaled(x, self.vector)
 
 
 class StreamPart(Part):

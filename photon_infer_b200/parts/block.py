@@ -12,28 +12,37 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from .base import Block, FeedForward, LayerCache, Mixer, Norm, Part, StepContext
+from .base import Block, ChannelScalePart, FeedForward, LayerCache, Mixer, Norm, Part, Scaled, StepContext
 from .registry import register_block
 
 
 class PreNormBlock(Block):
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, feed_forward: Optional[FeedForward] = None):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, feed_forward: Optional[FeedForward] = None,
+                 scale1: Optional[ChannelScalePart] = None, scale2: Optional[ChannelScalePart] = None):
         if (norm2 is None) != (feed_forward is None):
             raise ValueError("a pre-norm block has a second norm exactly when it has a feed-forward")
+        if scale2 is not None and feed_forward is None:
+            raise ValueError("a block without a feed-forward has no second channel scale")
         self.norm1, self._mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self.scale1, self.scale2 = scale1, scale2       # learned vectors on the two sublayers' outputs (layer scale)
 
     def parts(self) -> Dict[str, Part]:
         p = {"norm1": self.norm1, "mixer": self._mixer}
         if self.feed_forward is not None:
             p.update(norm2=self.norm2, feed_forward=self.feed_forward)
+        if self.scale1 is not None:
+            p["scale1"] = self.scale1
+        if self.scale2 is not None:
+            p["scale2"] = self.scale2
         return p
 
     def mixer(self) -> Mixer:
         return self._mixer
 
     def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
-        if isinstance(delta, (tuple, list)):
-            # the block before was a parallel one: the fused first kernels take one pending tensor
+        if isinstance(delta, (tuple, list, Scaled)):
+            # the block before was a parallel one, or its output waits with a channel scale: the fused first kernels
+            # take one plain pending tensor
             h = self.norm1.add_forward(delta, residual, ctx.dtype)
             a = self._mixer.forward(h, ctx, cache)
         # a part may take the residual sum and the norm into its first kernel (decode steps)
@@ -42,14 +51,16 @@ class PreNormBlock(Block):
         else:
             h = self.norm1.add_forward(delta, residual, ctx.dtype)
             a = self._mixer.forward(h, ctx, cache)
+        if self.scale1 is not None:
+            a = self.scale1.apply(a)
         if self.feed_forward is None:
             return residual, a                      # a layer without a feed-forward: the mixer's output stays pending
-        if self.feed_forward.fuses_norm(self.norm2, residual, ctx):
+        if not isinstance(a, Scaled) and self.feed_forward.fuses_norm(self.norm2, residual, ctx):
             d, residual = self.feed_forward.forward_with_norm(residual, a, self.norm2, ctx)
         else:
             h2 = self.norm2.add_forward(a, residual, ctx.dtype)
             d = self.feed_forward.forward(h2, ctx)
-        return residual, d
+        return residual, self.scale2.apply(d) if self.scale2 is not None else d
 
 
 class ParallelBlock(Block):

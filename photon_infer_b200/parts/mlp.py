@@ -1,6 +1,6 @@
 """Dense gated feed-forward: ``down(act(gate(h)) * up(h))``; with ``act`` silu it is SwiGLU
 (src/arch/transformer_block.cpp:282-291; include/photon/ops/kernels/swiglu_kernel.hpp:
-67-76), with the tanh form of gelu it is GeGLU.  Gate and up are one fused matrix on the
+67-76), with the tanh form of gelu it is GeGLU, with relu a ReLU-gated unit.  Gate and up are one fused matrix on the
 device, so ``h`` is read once.  The tensor names are parameters."""
 from __future__ import annotations
 
@@ -25,7 +25,7 @@ class SwiGLUFeedForward(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
         if activation not in ops.ACTIVATIONS:
-            raise ValueError(f"unknown activation {activation!r} (silu or gelu_tanh)")
+            raise ValueError(f"unknown activation {activation!r} (one of {sorted(ops.ACTIVATIONS)})")
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         self.activation = activation

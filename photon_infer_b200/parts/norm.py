@@ -9,24 +9,27 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from .base import Norm, TensorSpec, delta_pair
-from .registry import register_norm
+from .base import ChannelScalePart, Norm, TensorSpec, delta_terms
+from .registry import register_norm, register_scale
 
 
 class RMSNorm(Norm):
     kernel_modules = ("elementwise",)
 
-    def __init__(self, size: int, eps: float, weight_name: str = "weight"):
+    def __init__(self, size: int, eps: float, weight_name: str = "weight", scalar: bool = False):
         self.size = size
         self.eps = float(eps)
         self.weight_name = weight_name
+        self.scalar = bool(scalar)              # the weight is ONE number for all coordinates (a tensor without axes)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.weight_name, (self.size,), role="vector", init="norm")]
+        return [TensorSpec(self.weight_name, () if self.scalar else (self.size,), role="vector", init="norm")]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.weight_name]
+        w = tensors[self.weight_name]
+        # one number: the kernel reads a weight per coordinate, so the number is repeated (32-bit, exact)
+        self.weight = w.to(torch.float32).reshape(1).expand(self.size).contiguous() if self.scalar else w
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
@@ -36,14 +39,14 @@ class RMSNorm(Norm):
 
     def add_forward(self, delta, residual, out_dtype):
         out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
-        d1, d2 = delta_pair(delta)
-        ops.add_rmsnorm(d1, residual, self.weight, self.eps, out, delta2=d2)
+        d1, d2, sc = delta_terms(delta)
+        ops.add_rmsnorm(d1, residual, self.weight, self.eps, out, delta2=d2, delta_scale=sc)
         return out
 
     def add_forward_rows(self, delta, residual, rows, out_dtype):
         out = torch.empty((rows.numel(), residual.shape[1]), dtype=out_dtype, device=residual.device)
-        d1, d2 = delta_pair(delta)
-        ops.add_rmsnorm(d1, residual, self.weight, self.eps, out, rows=rows, delta2=d2)
+        d1, d2, sc = delta_terms(delta)
+        ops.add_rmsnorm(d1, residual, self.weight, self.eps, out, rows=rows, delta2=d2, delta_scale=sc)
         return out
 
 
@@ -77,16 +80,35 @@ class LayerNorm(Norm):
 
     def add_forward(self, delta, residual, out_dtype):
         out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
-        d1, d2 = delta_pair(delta)
-        ops.add_layernorm(d1, residual, self.weight, self.bias, self.eps, out, delta2=d2)
+        d1, d2, sc = delta_terms(delta)
+        ops.add_layernorm(d1, residual, self.weight, self.bias, self.eps, out, delta2=d2, delta_scale=sc)
         return out
 
     def add_forward_rows(self, delta, residual, rows, out_dtype):
         out = torch.empty((rows.numel(), residual.shape[1]), dtype=out_dtype, device=residual.device)
-        d1, d2 = delta_pair(delta)
-        ops.add_layernorm(d1, residual, self.weight, self.bias, self.eps, out, rows=rows, delta2=d2)
+        d1, d2, sc = delta_terms(delta)
+        ops.add_layernorm(d1, residual, self.weight, self.bias, self.eps, out, rows=rows, delta2=d2, delta_scale=sc)
         return out
 
 
+class ChannelScale(ChannelScalePart):
+    """``y = s * x`` with a learned vector ``s [size]`` (layer scale).  The product is formed in 32-bit inside the
+    norm kernel that adds the sublayer's output to the residual stream."""
+    kernel_modules = ("elementwise",)
+
+    def __init__(self, size: int, name: str = "scale"):
+        self.size, self.name = size, name
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.name, (self.size,), role="vector", init="norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.vector = tensors[self.name].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.vector.numel() * self.vector.element_size()
+
+
+register_scale("channel_scale", ChannelScale)
 register_norm("rms_norm", RMSNorm)
 register_norm("layer_norm", LayerNorm)

@@ -17,9 +17,10 @@ FEED_FORWARDS: Dict[str, Callable] = {}
 POSITION_ENCODINGS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
 STREAM_PARTS: Dict[str, Callable] = {}
+SCALES: Dict[str, Callable] = {}
 
 _TABLES = {"norm": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS,
-           "position_encoding": POSITION_ENCODINGS, "block": BLOCKS, "stream": STREAM_PARTS}
+           "position_encoding": POSITION_ENCODINGS, "block": BLOCKS, "stream": STREAM_PARTS, "scale": SCALES}
 
 
 def _register(table_name: str, kind: str, factory: Callable, replace: bool) -> None:
@@ -35,6 +36,7 @@ def register_feed_forward(kind, factory, replace=False): _register("feed_forward
 def register_position_encoding(kind, factory, replace=False): _register("position_encoding", kind, factory, replace)
 def register_block(kind, factory, replace=False): _register("block", kind, factory, replace)
 def register_stream_part(kind, factory, replace=False): _register("stream", kind, factory, replace)
+def register_scale(kind, factory, replace=False): _register("scale", kind, factory, replace)
 
 
 def create_part(table_name: str, kind: str, params: dict):
@@ -48,4 +50,5 @@ def create_part(table_name: str, kind: str, params: dict):
 
 
 def _ensure_builtin() -> None:
-    from . import attention, block, gla, latent_attention, mlp, moe, norm, normed_attention, rope, stream  # noqa: F401  (each registers itself)
+    from . import (attention, block, delta_rule, gla, latent_attention, mlp, moe, norm, normed_attention, rope,  # noqa: F401
+                   stream, talking_attention)                                       # (each registers itself)
