@@ -131,7 +131,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dic
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"cannot store dtype {t.dtype}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""   # reshape: a tensor without axes has bytes too
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
         blobs.append(raw)

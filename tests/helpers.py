@@ -311,3 +311,95 @@ def fekopel_plain_logits(folder: str, ids: Sequence[int]) -> torch.Tensor:
         cfg, tensors = fekopel_plain_model(folder)
         _fekopel_cache[key] = fekopel_plain.forward(cfg, tensors, list(ids))
     return _fekopel_cache[key]
+
+
+# ----------------------------------------------------------------------------- Lerosun
+
+def _latt(heads, kv_heads, dim, scale, size=None, rot=None):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=scale)
+    if size:
+        m["mask"] = dict(size=size)
+    if rot:
+        m["rot"] = dict(base=rot[0], dims=rot[1])
+    return m
+
+
+def _ldelta(heads, kv_heads, dim, vdim, conv):
+    return dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv)
+
+
+_dense = lambda ff: dict(kind="dense", ff=ff)
+
+# Tiny Lerosun configurations that differ in every size, in the order of the layers and in which optional pieces they
+# have.  Windows are short, so that prompts and decoded tokens alike pass their edges many times.
+TINY_LEROSUN: Dict[str, dict] = {
+    # a looped block in the middle; delta first; rotation of half a head; two windows
+    "ls_a": dict(
+        config=dict(architecture="Lerosun", vocab=150, width=64, norm=dict(eps=1e-5),
+                    layers=[dict(type="delta", mixer=_ldelta(4, 2, 16, 24, 4), mlp=_dense(96)),
+                            dict(type="attention", mixer=_latt(4, 2, 32, 0.2, 40, (5000.0, 16)), mlp=_dense(80)),
+                            dict(type="delta", mixer=_ldelta(2, 2, 32, 16, 3), mlp=None),
+                            dict(type="attention", mixer=_latt(2, 1, 64, 0.15, 24, (100.0, 64)), mlp=None)],
+                    loop=dict(start=1, stop=3, times=2)),
+        seed=31, init_std=0.1, norm_std=0.1, block_size=16),
+    # no loop; one key/value head for three query heads; a window of one page; a convolution of two taps; no rotation;
+    # one query/key head for four value heads; pages of 8
+    "ls_b": dict(
+        config=dict(architecture="Lerosun", vocab=210, width=96, norm=dict(eps=1e-6),
+                    layers=[dict(type="attention", mixer=_latt(3, 1, 16, 0.3, 8), mlp=_dense(40)),
+                            dict(type="delta", mixer=_ldelta(4, 1, 8, 8, 2), mlp=_dense(56)),
+                            dict(type="attention", mixer=_latt(4, 4, 24, 0.25, 19, (1e6, 8)), mlp=None)],
+                    loop=None),
+        seed=32, init_std=0.08, norm_std=0.15, block_size=8),
+    # the whole model is the looped block (three passes); no window at all; a wide delta head; a convolution of one
+    # tap (no rows to keep); pages of 32
+    "ls_c": dict(
+        config=dict(architecture="Lerosun", vocab=131, width=48, norm=dict(eps=2e-5),
+                    layers=[dict(type="attention", mixer=_latt(3, 3, 16, 0.25, None, (777.0, 4)), mlp=_dense(72)),
+                            dict(type="delta", mixer=_ldelta(1, 1, 72, 40, 1), mlp=None)],
+                    loop=dict(start=0, stop=2, times=3)),
+        seed=33, init_std=0.12, norm_std=0.05, block_size=32),
+    # a block that is "looped" once, at the end; heads of 128; a window longer than most requests; five taps
+    "ls_d": dict(
+        config=dict(architecture="Lerosun", vocab=90, width=32, norm=dict(eps=1e-5),
+                    layers=[dict(type="delta", mixer=_ldelta(2, 1, 128, 128, 5), mlp=_dense(24)),
+                            dict(type="attention", mixer=_latt(2, 1, 128, 0.09, 100, (300000.0, 32)), mlp=_dense(48))],
+                    loop=dict(start=1, stop=2, times=1)),
+        seed=34, init_std=0.15, norm_std=0.1, block_size=16),
+    # sizes that are multiples of nothing; a window of three keys; one head
+    "ls_e": dict(
+        config=dict(architecture="Lerosun", vocab=77, width=50, norm=dict(eps=1e-5),
+                    layers=[dict(type="attention", mixer=_latt(5, 5, 6, 0.4, 3, (50.0, 6)), mlp=_dense(30)),
+                            dict(type="delta", mixer=_ldelta(3, 3, 9, 33, 7), mlp=None),
+                            dict(type="attention", mixer=_latt(1, 1, 18, 0.2, 37), mlp=_dense(22)),
+                            dict(type="delta", mixer=_ldelta(6, 2, 18, 14, 4), mlp=_dense(70))],
+                    loop=dict(start=1, stop=4, times=2)),
+        seed=35, init_std=0.1, norm_std=0.1, block_size=16),
+}
+
+
+def make_lerosun_folder(path: str, name: str, dtype: str = "bfloat16") -> str:
+    from photon_infer_b200.weights import write_random_model
+    t = TINY_LEROSUN[name]
+    write_random_model(path, t["config"], seed=t["seed"], init_std=t["init_std"], norm_std=t["norm_std"], dtype=dtype)
+    return path
+
+
+_lerosun_cache: Dict[tuple, torch.Tensor] = {}
+_lerosun_models: Dict[str, tuple] = {}
+
+
+def lerosun_plain_model(folder: str):
+    from plain import lerosun_plain
+    if folder not in _lerosun_models:
+        _lerosun_models[folder] = lerosun_plain.read_folder(folder)
+    return _lerosun_models[folder]
+
+
+def lerosun_plain_logits(folder: str, ids: Sequence[int]) -> torch.Tensor:
+    from plain import lerosun_plain
+    key = (folder, tuple(ids))
+    if key not in _lerosun_cache:
+        cfg, tensors = lerosun_plain_model(folder)
+        _lerosun_cache[key] = lerosun_plain.forward(cfg, tensors, list(ids))
+    return _lerosun_cache[key]

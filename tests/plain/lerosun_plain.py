@@ -205,3 +205,10 @@ def read_folder(folder):
         t = torch.frombuffer(bytearray(data[a:b]), dtype=_DT[info["dtype"]]) if b > a else torch.zeros(0, dtype=_DT[info["dtype"]])
         tensors[name] = t.reshape(info["shape"]).clone()
     return cfg, tensors
+
+
+def greedy(config, tensors, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(torch.argmax(forward(config, tensors, ids)[-1])))
+    return ids[len(prompt):]
