@@ -1,6 +1,7 @@
-"""Prefill and decode throughput of another design (the Finelix or the Fekopel decoder) beside a Llama decoder of
-equal width, depth and feed-forward size (``python bench.py --design finelix|fekopel``), with the parts of a layer
-timed alone against their rooflines.
+"""Prefill and decode throughput of another design (the Finelix, the Fekopel or the Lerosun decoder) beside a Llama
+decoder of equal width, depth and feed-forward size (``python bench.py --design finelix|fekopel|lerosun``), with the
+parts of a layer timed alone against their rooflines.  The Lerosun decoder also runs beside the Finelix decoder, the
+other design with a recurrent mixer (a matrix of state per head) next to attention.
 
 Random weights drawn on the device, synthetic token ids, bfloat16.  Per size:
 
@@ -53,6 +54,22 @@ def fekopel_config(width: int, layers: int) -> dict:
                                              softcap=30.0), mlp=mlp)
     return dict(architecture="Fekopel", vocab=32000, width=width, norm=dict(eps=1e-5),
                 layers=[a2 if i % 2 == 0 else a1 for i in range(layers)], loop=None)
+
+
+LEROSUN_WINDOW = 1024
+
+
+def lerosun_config(width: int, layers: int) -> dict:
+    """Alternating layers of attention with mixed heads (heads of 128, a window of 1,024 keys, half of a head rotated,
+    a sink, an output gate; the values are the keys) and of the gated delta rule (heads of 128 x 128, two value heads
+    per query/key head, convolutions of four taps); dense feed-forwards of 4 x width with a relu gate."""
+    heads, kv = width // 128, max(1, width // 1024)
+    mlp = dict(kind="dense", ff=4 * width)
+    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5,
+                                            mask=dict(size=LEROSUN_WINDOW), rot=dict(base=10000.0, dims=64)), mlp=mlp)
+    delta = dict(type="delta", mixer=dict(heads=heads, kv_heads=heads // 2, dim=128, vdim=128, conv=4), mlp=mlp)
+    return dict(architecture="Lerosun", vocab=32000, width=width, norm=dict(eps=1e-5),
+                layers=[delta if i % 2 == 0 else att for i in range(layers)], loop=None)
 
 
 def llama_config(width: int, layers: int, window=None) -> dict:
@@ -122,14 +139,20 @@ def _mixer_numbers(m, kind: str, tokens: int, contexts) -> tuple:
         state = len(contexts) * m.heads * m.dim * m.vdim * 4 * 2
         flops = tokens * (w // 2) * 2 + 5 * tokens * m.heads * m.dim * m.vdim
         return state, flops
+    if kind == "delta":
+        # the state is read and written once a step; per token and state element: two read-outs, the decay and the write
+        state = len(contexts) * (m.heads * m.dim * m.vdim + (m.taps - 1) * m.channels) * 4 * 2
+        flops = tokens * (w // 2) * 2 + 7 * tokens * m.heads * m.dim * m.vdim
+        return state, flops
     reach = getattr(m, "window", None)
     reach = None if reach is None else reach + getattr(m, "keep_first", 0)
     seen_by = lambda p: p + 1 if reach is None else min(p + 1, reach)      # keys the token at position p reads
-    if kind in ("attention", "normed"):
+    if kind in ("attention", "normed", "talking"):
         pairs = sum(sum(seen_by(p) for p in range(c)) for c in contexts) if tokens > len(contexts) else sum(seen_by(c - 1) for c in contexts)
         held = sum(seen_by(c - 1) for c in contexts)
         dv = getattr(m, "value_dim", m.head_dim)
-        return held * m.n_kv * (m.head_dim + dv) * 2, tokens * (w // 2) * 2 + 2 * m.n_q * (m.head_dim + dv) * pairs
+        mix = 2 * m.n_q * m.n_q * pairs if kind == "talking" and m.talk else 0       # every head's score from all heads'
+        return held * m.n_kv * (m.head_dim + dv) * 2, tokens * (w // 2) * 2 + 2 * m.n_q * (m.head_dim + dv) * pairs + mix
     pairs = sum(c * (c + 1) // 2 for c in contexts) if tokens > len(contexts) else sum(contexts)
     if kind == "latent":
         rows = sum(contexts) * m.width * 2
@@ -141,10 +164,12 @@ def _mixer_numbers(m, kind: str, tokens: int, contexts) -> tuple:
 def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
     """The mixer and the feed-forward of the first layer of every kind, alone, in a prefill step and a decode step."""
     from ..parts.attention import PagedAttention
+    from ..parts.delta_rule import GatedDeltaRule
     from ..parts.gla import GatedLinearAttention
     from ..parts.latent_attention import LatentAttention
     from ..parts.moe import MoEFeedForward
     from ..parts.normed_attention import NormedAttention
+    from ..parts.talking_attention import TalkingAttention
     model, cache = runner.model, runner.cache
     H = model.spec.hidden_size
     out: Dict[str, dict] = {}
@@ -170,7 +195,7 @@ def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
             block = model.blocks[e.layer]
             m = block.mixer()
             kind = {GatedLinearAttention: "gla", LatentAttention: "latent", PagedAttention: "attention",
-                    NormedAttention: "normed"}.get(type(m))
+                    NormedAttention: "normed", TalkingAttention: "talking", GatedDeltaRule: "delta"}.get(type(m))
             if kind == "normed":                     # the two kinds of layer are timed apart
                 kind_name = "normed_gated" if m.output_gate else "normed_sink"
             else:
@@ -249,14 +274,18 @@ def run_design_comparison(design: str, args, hbm_peak: float, tf_peak: float, pe
     from ..engine.runner import ModelRunner
     steps, warmup = max(8, min(args.steps, 64)), max(args.warmup, 3)
     layers = {2048: 8, 4096: 4}
-    make, window = {"finelix": (finelix_config, None), "fekopel": (fekopel_config, FEKOPEL_WINDOW)}[design]
+    make, window = {"finelix": (finelix_config, None), "fekopel": (fekopel_config, FEKOPEL_WINDOW),
+                    "lerosun": (lerosun_config, LEROSUN_WINDOW)}[design]
     line = {"design": design, "dtype": args.dtype, "data": "synthetic", "peaks": peak_src,
             "workload": {"prefill_tokens": PREFILL, "decode_batch": BATCH, "decode_context": PROMPT, "steps": steps,
                          "warmup": warmup}, "sizes": {}}
     for width in [int(w) for w in args.design_sizes.split(",") if w]:
         n_layers = layers.get(width, 4)
         point = {"layers": n_layers}
-        for name, cfg in ((design, make(width, n_layers)), ("llama", llama_config(width, n_layers, window))):
+        models = [(design, make(width, n_layers)), ("llama", llama_config(width, n_layers, window))]
+        if design == "lerosun":
+            models.append(("finelix", finelix_config(width, n_layers)))
+        for name, cfg in models:
             print(f"[bench] {name} width {width}, {n_layers} layers", file=sys.stderr, flush=True)
             model = random_model(cfg, args.dtype, seed=0)
             options = EngineOptions(dtype=args.dtype, block_size=args.block_size,
