@@ -317,3 +317,18 @@ PHOTON_API int photon_talk_attention(const void* q, long q_stride, void* out, lo
   if (dtype == PHOTON_BF16) TALK_GO(bf16);
   return PHOTON_ERR_ARGUMENT;
 }
+
+// The shares of a token's splits, part float [T][splits][H][d + 2] (per head: the running maximum as a natural
+// logarithm, the sum, the d weighted sums), merged in split order; then the sink, the gate and the division.
+PHOTON_API int photon_talk_merge(const float* part, int splits, void* out, long out_stride, int dtype, int T, int H, int d,
+                                 const float* sink, const float* gate, long gate_stride, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (part == nullptr || splits < 1 || H <= 0 || d <= 0) return PHOTON_ERR_ARGUMENT;
+  if (dtype == PHOTON_F32)
+    return launch_pdl(talk_merge_kernel<float>, dim3(T), dim3(TALK_THREADS), 0, stream, part, splits, (float*)out, out_stride, H, d,
+                      sink, gate, gate_stride);
+  if (dtype == PHOTON_BF16)
+    return launch_pdl(talk_merge_kernel<bf16>, dim3(T), dim3(TALK_THREADS), 0, stream, part, splits, (bf16*)out, out_stride, H, d,
+                      sink, gate, gate_stride);
+  return PHOTON_ERR_ARGUMENT;
+}

@@ -182,7 +182,8 @@ def ensure_built(modules: Iterable[object]) -> None:
 # specialisations that the build check compiles besides the plain modules (the Llama 3.2 1B shape)
 DEFAULT_SPECIALISATIONS = (("attention_flash", {"HEAD_DIM": 64}), ("attention_tc", {"HEAD_DIM": 64}),
                            ("attention_decode", {"HEAD_DIM": 64}), ("attention_flash", {"HEAD_DIM": 128}),
-                           ("attention_tc", {"HEAD_DIM": 128}), ("attention_decode", {"HEAD_DIM": 128}))
+                           ("attention_tc", {"HEAD_DIM": 128}), ("attention_decode", {"HEAD_DIM": 128}),
+                           ("attention_talk_mma", {"HEAD_DIM": 128, "TALK_H": 16, "TALK_G": 2}))
 
 
 def build_all(verbose: bool = False) -> None:

@@ -86,94 +86,103 @@ __global__ void delta_conv_state_kernel(const TI* __restrict__ x, long x_stride,
 }
 
 // ---------------------------------------------------------------- the recurrence
-// One block per (request, head).  Thread j * RP + r holds rows r * RPT .. of value column j; the RP partial sums of a
-// column lie in neighbouring lanes and meet by shuffles.  The inputs of CH tokens are staged in shared memory (the next
-// chunk's are fetched into registers while the current one is computed), so the walk meets one barrier per chunk.
+// The columns of a head's state never meet: column j needs k, q, the two per-head numbers and v_j alone.  So one block
+// owns `vcols` neighbouring columns of one (request, head), and the launcher cuts a head into as many groups of columns
+// as fill the GPU.  Thread jl * RP + r holds rows r * RPT .. of its column in registers; the RP partial sums of a column
+// lie in neighbouring lanes and meet by shuffles, in an order that depends on (RPT, RP) alone, which the launcher
+// picks from dim alone: a column's arithmetic is the same chain however the head was cut and whatever else the
+// step holds.  The inputs of CH tokens are staged in shared memory (the next chunk's are fetched into registers while
+// the current one is computed), so the walk meets one barrier per chunk.
 #define DELTA_CH 8
+#define DELTA_FETCH 4                                    // values of a token's row that a thread fetches
 
-// The widest block a row count allows: a thread with many rows of state needs many registers.
-constexpr int delta_max_threads(int rpt) { return rpt >= 64 ? 256 : (rpt >= 32 ? 512 : 1024); }
-static inline int delta_tok_floats(int dimp, int vdim) { return 2 * dimp + ((vdim + 2 + 3) & ~3); }   // rows stay 16-byte aligned
+static inline int delta_tok_floats(int dimp, int vcols) { return 2 * dimp + ((vcols + 3) & ~3) + 4; }   // rows stay 16-byte aligned
 
 template <int RPT, int RP>
-__global__ void __launch_bounds__(delta_max_threads(RPT))
+__global__ void __launch_bounds__(256)
 delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_stride, int ab_dtype_bf16,
                        const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                        const int* __restrict__ cu_tokens, const int* __restrict__ state_slots, float* __restrict__ state,
-                       long state_stride, int num_slots, float* __restrict__ o_out, int Gq, int H, int dim, int vdim, int* err) {
+                       long state_stride, int num_slots, float* __restrict__ o_out, int Gq, int H, int dim, int vdim, int vcols,
+                       int* err) {
   extern __shared__ __align__(16) float sm[];
   pdl_wait();
-  const int s = blockIdx.x, h = blockIdx.y;
+  const int s = blockIdx.x, h = blockIdx.y, cg = blockIdx.z;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int t0 = cu_tokens[s], t1 = cu_tokens[s + 1];
   if (t1 <= t0) return;
   const int slot = state_slots[s];
   if (slot >= num_slots) {
-    if (tid == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t0, slot, num_slots);
+    if (tid == 0 && cg == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t0, slot, num_slots);
     return;
   }
   const int C = 2 * Gq * dim + H * vdim;
-  const int dimp = RPT * RP;                              // rows padded to whole groups; the padding stays zero
-  const int j = tid / RP, r = tid % RP;
-  const bool active = j < vdim;
+  constexpr int dimp = RPT * RP;                          // rows padded to whole groups; the padding stays zero
+  const int jl = tid / RP, r = tid % RP;
+  const int j = cg * vcols + jl;                          // the thread's column of the head
+  const bool active = jl < vcols && j < vdim;
   const int hq = h / (H / Gq);
   const int row0 = r * RPT;
   float* S = slot >= 0 ? state + (size_t)slot * state_stride + (size_t)h * dim * vdim : nullptr;
   float st[RPT];
 #pragma unroll
   for (int i = 0; i < RPT; ++i) st[i] = (S != nullptr && active && row0 + i < dim) ? S[(size_t)(row0 + i) * vdim + j] : 0.f;
-  // a chunk in shared memory: q [CH][dimp], k [CH][dimp], v [CH][vdim], g [CH], beta [CH]; two buffers
-  const int per_tok = 2 * dimp + ((vdim + 2 + 3) & ~3);
+  // a token in shared memory: q [dimp], k [dimp], v [vcols, padded to 4], g, beta; CH tokens a buffer, two buffers
+  const int vpad = (vcols + 3) & ~3;
+  const int per_tok = 2 * dimp + vpad + 4;
   const int buf_floats = DELTA_CH * per_tok;
   for (int i = tid; i < 2 * buf_floats; i += nthreads) sm[i] = 0.f;
   const float decay_rate = expf(a_log[h]), bias = dt_bias[h];
-  const int per_chunk = DELTA_CH * (2 * dim + vdim + 2);  // values a chunk brings
-  constexpr int MAXV = 8;                                 // values a thread fetches per chunk (checked by the launcher)
-  float pre[MAXV];
+  // what this thread brings of every token: up to DELTA_FETCH numbers of q | k | the block's columns of v
+  const int rowlen = 2 * dim + vcols;
+  int src_col[DELTA_FETCH], dst_at[DELTA_FETCH];
+#pragma unroll
+  for (int n = 0; n < DELTA_FETCH; ++n) {
+    const int w = tid + n * nthreads;
+    src_col[n] = -1; dst_at[n] = 0;
+    if (w < dim) { src_col[n] = hq * dim + w; dst_at[n] = w; }
+    else if (w < 2 * dim) { src_col[n] = (Gq + hq) * dim + (w - dim); dst_at[n] = dimp + (w - dim); }
+    else if (w < rowlen && cg * vcols + (w - 2 * dim) < vdim) {
+      src_col[n] = 2 * Gq * dim + h * vdim + cg * vcols + (w - 2 * dim); dst_at[n] = 2 * dimp + (w - 2 * dim);
+    }
+  }
+  float pre[DELTA_CH][DELTA_FETCH];
+  float pre_ab = 0.f;                                     // threads 0 .. 2 CH - 1: a token's decay or step size
   auto fetch = [&](int c0) {
 #pragma unroll
-    for (int n = 0; n < MAXV; ++n) {
-      const int e = tid + n * nthreads;
+    for (int tt = 0; tt < DELTA_CH; ++tt) {
+      const bool live = c0 + tt < t1;
+      const float* row = y + (size_t)(c0 + tt) * C;
+#pragma unroll
+      for (int n = 0; n < DELTA_FETCH; ++n) pre[tt][n] = (live && src_col[n] >= 0) ? row[src_col[n]] : 0.f;
+    }
+    if (tid < 2 * DELTA_CH) {
+      const int t = c0 + (tid >> 1), which = tid & 1;
       float v = 0.f;
-      if (e < per_chunk) {
-        const int tt = e / (2 * dim + vdim + 2), w = e - tt * (2 * dim + vdim + 2);
-        const int t = c0 + tt;
-        if (t < t1) {
-          const float* row = y + (size_t)t * C;
-          if (w < dim) v = row[hq * dim + w];
-          else if (w < 2 * dim) v = row[(Gq + hq) * dim + (w - dim)];
-          else if (w < 2 * dim + vdim) v = row[2 * Gq * dim + h * vdim + (w - 2 * dim)];
-          else {
-            // the two per-head numbers of the token: raw decay input, then raw beta input
-            const int which = w - 2 * dim - vdim;
-            const size_t at = (size_t)t * ab_stride + (which == 0 ? h : H + h);
-            const float raw = ab_dtype_bf16 ? __bfloat162float(((const bf16*)x_ab)[at]) : x_ab[at];
-            if (which == 0) {
-              const float z = raw + bias;
-              const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));       // softplus
-              v = expf(-decay_rate * sp);
-            } else {
-              v = 1.0f / (1.0f + expf(-raw));
-            }
-          }
+      if (t < t1) {
+        // the two per-head numbers of the token: raw decay input, then raw beta input
+        const size_t at = (size_t)t * ab_stride + (which == 0 ? h : H + h);
+        const float raw = ab_dtype_bf16 ? __bfloat162float(((const bf16*)x_ab)[at]) : x_ab[at];
+        if (which == 0) {
+          const float z = raw + bias;
+          const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));       // softplus
+          v = expf(-decay_rate * sp);
+        } else {
+          v = 1.0f / (1.0f + expf(-raw));
         }
       }
-      pre[n] = v;
+      pre_ab = v;
     }
   };
   auto stash = [&](int buf) {
     float* b = sm + buf * buf_floats;
 #pragma unroll
-    for (int n = 0; n < MAXV; ++n) {
-      const int e = tid + n * nthreads;
-      if (e < per_chunk) {
-        const int tt = e / (2 * dim + vdim + 2), w = e - tt * (2 * dim + vdim + 2);
-        float* tok = b + tt * per_tok;
-        if (w < dim) tok[w] = pre[n];
-        else if (w < 2 * dim) tok[dimp + (w - dim)] = pre[n];
-        else tok[2 * dimp + (w - 2 * dim)] = pre[n];
-      }
+    for (int tt = 0; tt < DELTA_CH; ++tt) {
+#pragma unroll
+      for (int n = 0; n < DELTA_FETCH; ++n)
+        if (src_col[n] >= 0) b[tt * per_tok + dst_at[n]] = pre[tt][n];
     }
+    if (tid < 2 * DELTA_CH) b[(tid >> 1) * per_tok + 2 * dimp + vpad + (tid & 1)] = pre_ab;
   };
   __syncthreads();
   fetch(t0);
@@ -188,8 +197,8 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
       const float* tok = b + tt * per_tok;
       const float4* q4 = reinterpret_cast<const float4*>(tok + row0);
       const float4* k4 = reinterpret_cast<const float4*>(tok + dimp + row0);
-      const float vj = active ? tok[2 * dimp + j] : 0.f;
-      const float g = tok[2 * dimp + vdim], beta = tok[2 * dimp + vdim + 1];
+      const float vj = active ? tok[2 * dimp + jl] : 0.f;
+      const float g = tok[2 * dimp + vpad], beta = tok[2 * dimp + vpad + 1];
       float p1 = 0.f, p2 = 0.f, kq = 0.f;
 #pragma unroll
       for (int i = 0; i < RPT / 4; ++i) {
@@ -280,23 +289,34 @@ static int delta_recurrent_launch(const float* y, const void* ab, long ab_stride
                                   const float* dt_bias, const int* cu_tokens, const int* state_slots, float* state,
                                   long state_stride, int num_slots, float* o, int S, int Gq, int H, int dim, int vdim, int* err,
                                   cudaStream_t stream) {
-  // enough threads for the columns, and for fetching a chunk's inputs with at most 8 values a thread
-  const int fetchers = (DELTA_CH * (2 * dim + vdim + 2) + 7) / 8;
-  const int threads = ((max(vdim * RP, fetchers) + 31) / 32) * 32;
-  const int dimp = RPT * RP;
-  const size_t smem = (size_t)2 * DELTA_CH * delta_tok_floats(dimp, vdim) * sizeof(float);
-  if (threads > delta_max_threads(RPT) || smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  // Columns a block owns: at most 256 / RP, and few enough that the step's blocks fill the GPU about twice; a multiple
+  // of 8 where the head has that many.  The cut changes no column's arithmetic.
+  const int most = 256 / RP;
+  const long heads = (long)S * H;
+  int groups = (int)((2L * photon_sm_count() + heads - 1) / heads);
+  if (groups < 1) groups = 1;
+  int vcols = (vdim + groups - 1) / groups;
+  vcols = ((vcols + 7) / 8) * 8;
+  if (vcols > most) vcols = most;
+  if (vcols > vdim) vcols = vdim;
+  groups = (vdim + vcols - 1) / vcols;
+  // enough threads for the columns, and for fetching a token's row with at most DELTA_FETCH values a thread
+  const int fetchers = (2 * dim + vcols + DELTA_FETCH - 1) / DELTA_FETCH;
+  int threads = ((max(max(vcols * RP, fetchers), 2 * DELTA_CH) + 31) / 32) * 32;
+  if (threads > 256 || groups > 65535) return PHOTON_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)2 * DELTA_CH * delta_tok_floats(RPT * RP, vcols) * sizeof(float);
+  if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_recurrent_kernel<RPT, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_pdl(delta_recurrent_kernel<RPT, RP>, dim3(S, H), dim3(threads), smem, stream, y, (const float*)ab, ab_stride, ab_bf16,
-                    a_log, dt_bias, cu_tokens, state_slots, state, state_stride, num_slots, o, Gq, H, dim, vdim, err);
+  return launch_pdl(delta_recurrent_kernel<RPT, RP>, dim3(S, H, groups), dim3(threads), smem, stream, y, (const float*)ab, ab_stride,
+                    ab_bf16, a_log, dt_bias, cu_tokens, state_slots, state, state_stride, num_slots, o, Gq, H, dim, vdim, vcols, err);
 }
 
 // y float [T][C] from photon_delta_conv; ab [T][>= 2 H] of ab_dtype (row stride ab_stride): the raw decay inputs of the
 // H heads, then the raw beta inputs; a_log, dt_bias float [H]; state as above with S [H][dim][vdim] at its start;
-// o float [T][H * vdim]: the read-outs before the norm.
+// o float [T][H * vdim]: the read-outs before the norm.  dim up to 256.
 PHOTON_API int photon_delta_recurrent(const float* y, const void* ab, long ab_stride, int ab_dtype, const float* a_log,
                                       const float* dt_bias, const int* cu_tokens, const int* state_slots, float* state,
                                       long state_stride, int num_slots, float* o, int S, int Gq, int H, int dim, int vdim,
@@ -306,14 +326,11 @@ PHOTON_API int photon_delta_recurrent(const float* y, const void* ab, long ab_st
   if (ab_dtype != PHOTON_F32 && ab_dtype != PHOTON_BF16) return PHOTON_ERR_ARGUMENT;
   if (S > 2147483647 / 2 || H > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int bf = ab_dtype == PHOTON_BF16;
-  // lanes per column (RP, a power of two up to 32) and rows per lane (RPT, a multiple of 4): the block stays within
-  // 1024 threads and a thread within 32 rows of state where the sizes allow it
-#define DELTA_TRY(RPT, RP) if (dim <= RPT * RP && vdim * RP <= delta_max_threads(RPT) && \
-                               (DELTA_CH * (2 * dim + vdim + 2) + 7) / 8 <= delta_max_threads(RPT)) \
+  // lanes per column (RP) and rows per lane (RPT, a multiple of 4) follow from dim alone
+#define DELTA_TRY(RPT, RP) if (dim <= RPT * RP) \
     return delta_recurrent_launch<RPT, RP>(y, ab, ab_stride, bf, a_log, dt_bias, cu_tokens, state_slots, state, state_stride, num_slots, \
                                            o, S, Gq, H, dim, vdim, err, stream)
-  DELTA_TRY(4, 4); DELTA_TRY(8, 4); DELTA_TRY(8, 8); DELTA_TRY(16, 4); DELTA_TRY(16, 8); DELTA_TRY(32, 4); DELTA_TRY(32, 8);
-  DELTA_TRY(16, 16); DELTA_TRY(32, 2); DELTA_TRY(64, 4); DELTA_TRY(64, 2); DELTA_TRY(64, 1); DELTA_TRY(128, 1); DELTA_TRY(128, 2);
+  DELTA_TRY(4, 4); DELTA_TRY(8, 4); DELTA_TRY(8, 8); DELTA_TRY(16, 8); DELTA_TRY(32, 8);
   return PHOTON_ERR_UNSUPPORTED;
 }
 

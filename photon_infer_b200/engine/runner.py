@@ -219,6 +219,10 @@ class ModelRunner:
                 grp = cache.groups[g]
                 ps = grp.page_size
                 seg(7 + g)[:] = [grp.tables[r][p // ps] * ps + p % ps for r, p in zip(rids, starts)]
+                if stateless_from is not None:
+                    # a padding row repeats a request's token but starts from a zero state, so behind a mixer with state
+                    # its keys and values differ from the request's own: it must not store them in the request's place
+                    seg(7 + g)[stateless_from:] = -1
                 cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
         else:
             t = 0

@@ -206,6 +206,21 @@ PHOTON_EXPORT int photon_talk_attention(const void* q, long q_stride, void* out,
                           const float* qmul, const float* talk, const float* sink, const float* gate, long gate_stride,
                           int splits, float* part, int* err, cudaStream_t stream);
 
+/* Merges the shares that a token's splits left in part [T][splits][H][d + 2] (maximum as a natural logarithm, sum, d
+ * weighted sums) in split order; then sink, gate and the division.  out [T][H * d] of dtype. */
+PHOTON_EXPORT int photon_talk_merge(const float* part, int splits, void* out, long out_stride, int dtype, int T, int H, int d,
+                      const float* sink, const float* gate, long gate_stride, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ attention_talk_mma.cu: the same attention on the tensor cores */
+/* bfloat16; the module is compiled for one (H, G, d) with -DTALK_H, -DTALK_G, -DHEAD_DIM and refuses others.  One block
+ * per 16 neighbouring tokens of a request (cu_tokens [S + 1], at most max_tokens tokens a request) with all heads; splits >
+ * 1: every split leaves its share in part [T * splits * H * (d + 2)] for photon_talk_merge and out is not written. */
+PHOTON_EXPORT int photon_talk_mma(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
+                    const int* block_table, int max_pages, const int* cu_tokens, const int* positions, int S, int max_tokens,
+                    int H, int G, int d, int page_size, int num_pages, int window, const float* qmul, const float* talk,
+                    const float* sink, const float* gate, long gate_stride, int splits, float* part, int* err,
+                    cudaStream_t stream);
+
 /* ------------------------------------------------------------------ gla.cu: gated linear attention (recurrent state) */
 /* Per (request, head): S = diag(a_t) S + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau), z_t = w_a2 low_t + b_a2, o_t = S^T (q_t *
  * qscale); out = o_t / rms(o_t) * norm_w * silu(g_t).  q, k [T][heads * dim], v, g [T][heads * vdim] and low [T][rank] share

@@ -1288,6 +1288,62 @@ def talk_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
              int(splits), _ptr(part), _ptr(err), _stream()), "talk_attention")
 
 
+def talk_mma_supported(n_q: int, n_kv: int, d: int) -> bool:
+    """Whether the tensor-core kernel of ``talk_attention_mma`` can be compiled for these sizes: the head size a
+    multiple of 16 up to 256, the accumulators of a warp's heads within its registers, shared memory for a tile of 32
+    keys.  Mirrors the static checks of ``attention_talk_mma.cu``."""
+    if d % 16 or not 16 <= d <= 256 or n_kv <= 0 or n_q % n_kv:
+        return False
+    warps = max(4, n_q) if n_q <= 8 else 16
+    heads_per_warp = -(-n_q // warps)
+    if heads_per_warp * d > (128 if warps > 8 else 256):
+        return False
+    smem = lambda bn: n_q * 16 * (d + 8) * 2 + 2 * n_kv * bn * (d + 8) * 2 + n_q * 16 * (bn + 8) * 4 + n_q * ((n_q + 3) & ~3) * 4 + 128
+    return smem(32) <= 226 * 1024
+
+
+def talk_attention_mma(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                       cu_tokens: torch.Tensor, positions: torch.Tensor, num_seqs: int, max_tokens: int, n_q: int, n_kv: int,
+                       d: int, window: Optional[int], qmul: torch.Tensor, talk: Optional[torch.Tensor],
+                       sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], err: Optional[torch.Tensor],
+                       splits: int = 1) -> None:
+    """``talk_attention`` on the tensor cores (bfloat16): one block per 16 neighbouring tokens of a request with all
+    heads; raw scores and weighted sums as mma.m16n8k16 with 32-bit sums, the mixing of the heads' scores and the
+    softmax in 32-bit.  ``splits`` > 1 shares a token's key tiles out over that many blocks, merged in split order."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, qmul, talk, sink, gate, err)
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or not talk_mma_supported(n_q, n_kv, d):
+        raise PhotonError(ErrorCode.UNSUPPORTED, "talk_attention_mma: bfloat16 and sizes that talk_mma_supported accepts")
+    if q.shape != (T, n_q * d) or q.stride(1) != 1 or out.shape != (T, n_q * d) or out.stride(1) != 1 or out.dtype != q.dtype:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention_mma: q and out must be [T, n_q * d] of one type")
+    if k_cache.dim() != 4 or k_cache.shape[1] != n_kv or k_cache.shape[3] != d or v_cache.shape != k_cache.shape \
+            or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention_mma: caches must be [pages, n_kv, page, d] of q's type")
+    for t_, n in ((qmul, n_q), (talk, n_q * n_q), (sink, n_q)):
+        if t_ is not None and (t_.dtype != torch.float32 or t_.numel() != n or not t_.is_contiguous()):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention_mma: qmul, talk and sink must be contiguous float32")
+    if gate is not None and (gate.shape != (T, n_q) or gate.dtype != torch.float32 or gate.stride(1) != 1):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "talk_attention_mma: gate must be float32 [T, n_q]")
+    for t_, what in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (positions, "positions")):
+        _int32(t_, what)
+    part = talk_scratch(q.device, T * splits * n_q * (d + 2)) if splits > 1 else None
+    defines = {"HEAD_DIM": d, "TALK_H": n_q, "TALK_G": n_kv}
+    f = _fn("attention_talk_mma", "photon_talk_mma",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_void_p,
+             c_void_p], defines=defines)
+    gate_stride = gate.stride(0) if gate is not None else 0
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(cu_tokens), _ptr(positions), int(num_seqs), int(max_tokens), n_q, n_kv, d,
+             k_cache.shape[2], k_cache.shape[0], int(window or 0), _ptr(qmul), _ptr(talk), _ptr(sink), _ptr(gate), gate_stride,
+             int(splits), _ptr(part), _ptr(err), _stream()), "talk_attention_mma")
+    if splits > 1:
+        m = _fn("attention_talk", "photon_talk_merge",
+                [c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p])
+        _check(m(_ptr(part), int(splits), _ptr(out), out.stride(0), _dtype_code(out), T, n_q, d, _ptr(sink), _ptr(gate),
+                 gate_stride, _stream()), "talk_merge")
+
+
 # ----------------------------------------------------------------------------- gated linear attention
 
 def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, low: torch.Tensor,

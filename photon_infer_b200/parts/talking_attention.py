@@ -49,6 +49,8 @@ class TalkingAttention(Mixer):
         self.w_in: Optional[torch.Tensor] = None        # [W_q; W_k; (W_v); (W_g)]
         self.w_o: Optional[torch.Tensor] = None
         self.q_bias = self.k_bias = self.qmul = self.talk_w = self.sink_w = self.inv_freq = None
+        # bfloat16 steps run on the tensor cores when the sizes allow it, else (and in 32-bit) the general kernel
+        self._tensor_cores = ops.talk_mma_supported(n_q_heads, n_kv_heads, head_dim)
 
     @property
     def _sections(self):
@@ -59,6 +61,8 @@ class TalkingAttention(Mixer):
         mods = list(self.kernel_modules)
         if dtype == torch.bfloat16:
             mods.extend(["gemm_skinny", "gemm_tc", "gemm_tc2"])
+            if self._tensor_cores:
+                mods.append(("attention_talk_mma", {"HEAD_DIM": self.head_dim, "TALK_H": self.n_q, "TALK_G": self.n_kv}))
         return mods
 
     def tensor_specs(self) -> List[TensorSpec]:
@@ -135,6 +139,11 @@ class TalkingAttention(Mixer):
             # run keeps one order of sums whatever the step)
             keys = ctx.max_context_len if self.window is None else min(self.window + 1, ctx.max_context_len)
             splits = max(1, min(keys // 128, (2 * ops.sm_count(q.device)) // max(1, ctx.num_tokens), 64))
+        if q.dtype == torch.bfloat16 and self._tensor_cores:
+            ops.talk_attention_mma(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions, ctx.num_seqs,
+                                   ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window, self.qmul, self.talk_w,
+                                   self.sink_w, gate, ctx.error_flag, splits=splits)
+            return
         ops.talk_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions, self.n_q, self.n_kv,
                            self.head_dim, self.window, self.qmul, self.talk_w, self.sink_w, gate, ctx.error_flag, splits=splits)
 

@@ -38,6 +38,7 @@ def test_c_program_links_against_the_libraries(tmp_path):
     cuda_home = os.path.dirname(os.path.dirname(find_nvcc()))
     libs = [compile_module(m) for m in ALL_MODULES]
     libs += [compile_module(m, {"HEAD_DIM": 64}) for m in ("attention_flash", "attention_tc", "attention_decode")]
+    libs.append(compile_module("attention_talk_mma", {"HEAD_DIM": 64, "TALK_H": 4, "TALK_G": 2}))
     names = _declared()
     src = tmp_path / "use_header.c"
     src.write_text(

@@ -150,7 +150,7 @@ class _Step:
         self.table = [[order[s * per + i] if i * page < lengths[s] else -1 for i in range(per)] for s in range(S)]
         self.pos = [list(range(L - n, L)) for L, n in zip(lengths, counts)]
 
-    def run(self, window, qmul, talk, sink, use_gate, splits=1):
+    def run(self, window, qmul, talk, sink, use_gate, splits=1, mma=False):
         from photon_infer_b200.kernels import ops
         H, G, d = self.dims
         for s, L in enumerate(self.lengths):
@@ -171,8 +171,14 @@ class _Step:
             gate = wide[:, 3:3 + H]
         err = torch.zeros(4, dtype=torch.int32, device=DEV)
         f = lambda t: None if t is None else t.float().contiguous().to(DEV)
-        ops.talk_attention(q, out, self.kc.to(DEV), self.vc.to(DEV), bt, seq, pos, H, G, d, window, f(qmul), f(talk), f(sink), gate, err,
-                           splits=splits)
+        if mma:
+            assert ops.talk_mma_supported(H, G, d)
+            cu = i32([sum(self.counts[:s]) for s in range(len(self.counts) + 1)])
+            ops.talk_attention_mma(q, out, self.kc.to(DEV), self.vc.to(DEV), bt, cu, pos, len(self.counts), max(self.counts), H, G, d,
+                                   window, f(qmul), f(talk), f(sink), gate, err, splits=splits)
+        else:
+            ops.talk_attention(q, out, self.kc.to(DEV), self.vc.to(DEV), bt, seq, pos, H, G, d, window, f(qmul), f(talk), f(sink), gate,
+                               err, splits=splits)
         torch.cuda.synchronize()
         assert err.cpu().tolist()[0] == 0
         return out.float().cpu()
@@ -206,20 +212,46 @@ def test_attention_with_mixed_heads(rule, heads, dtype, d, page):
     assert rel_err(got, want) < (1e-5 if dtype == torch.float32 else 2e-2)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rule", RULES, ids=lambda r: f"w{r['window']}t{int(r['talk'])}s{int(r['sink'])}g{int(r['gate'])}")
+@pytest.mark.parametrize("heads", [(2, 1), (6, 2), (8, 1), (5, 5), (1, 1), (16, 2), (12, 4), (20, 5)])
+@pytest.mark.parametrize("d,page", [(16, 8), (64, 16), (128, 32), (48, 24)])
+def test_attention_with_mixed_heads_on_the_tensor_cores(rule, heads, d, page):
+    """The bfloat16 kernel that owns 16 tokens with all their heads: portions that end inside a tile of 16 rows, single
+    tokens, the first token, pages smaller than a key tile and pages that do not divide it."""
+    from photon_infer_b200.kernels import ops
+    H, G = heads
+    if not ops.talk_mma_supported(H, G, d):
+        pytest.skip("the general kernel takes these sizes")
+    st = _Step(LENGTHS, COUNTS, H, G, d, page, torch.bfloat16, seed=H * 100 + d, std=1.0 if d < 64 else 0.5)
+    g = torch.Generator().manual_seed(H)
+    qmul = (0.5 + torch.rand(H, generator=g)) / math.sqrt(d)
+    talk = (torch.eye(H) + 0.4 * torch.randn(H, H, generator=g)) if rule["talk"] else None
+    sink = torch.randn(H, generator=g) if rule["sink"] else None
+    got = st.run(rule["window"], qmul, talk, sink, rule["gate"], mma=True)
+    assert rel_err(got, st.want(rule["window"], qmul, talk, sink, rule["gate"])) < 2e-2
+
+
+def test_the_tensor_core_kernel_accepts_what_it_can_hold():
+    from photon_infer_b200.kernels import ops
+    assert ops.talk_mma_supported(16, 2, 128) and ops.talk_mma_supported(8, 2, 256) and ops.talk_mma_supported(32, 4, 64)
+    assert not ops.talk_mma_supported(4, 2, 24) and not ops.talk_mma_supported(32, 4, 128) and not ops.talk_mma_supported(6, 4, 64)
+
+
+@pytest.mark.parametrize("dtype,mma", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
 @pytest.mark.parametrize("splits", [2, 5, 64])
 @pytest.mark.parametrize("window", [None, 130, 40])
-def test_attention_with_keys_split_over_blocks(dtype, splits, window):
+def test_attention_with_keys_split_over_blocks(dtype, mma, splits, window):
     st = _Step([300, 7, 129, 1], [1, 1, 1, 1], 6, 3, 32, 16, dtype, seed=splits)
     g = torch.Generator().manual_seed(3)
     qmul, talk, sink = torch.full((6,), 0.2), torch.eye(6) + 0.3 * torch.randn(6, 6, generator=g), torch.randn(6, generator=g)
-    got = st.run(window, qmul, talk, sink, True, splits=splits)
+    got = st.run(window, qmul, talk, sink, True, splits=splits, mma=mma)
     assert rel_err(got, st.want(window, qmul, talk, sink, True)) < (1e-5 if dtype == torch.float32 else 2e-2)
 
 
-@pytest.mark.parametrize("dtype,d,page", [(torch.float32, 12, 8), (torch.bfloat16, 64, 16)])
+@pytest.mark.parametrize("dtype,d,page,mma", [(torch.float32, 12, 8, False), (torch.bfloat16, 64, 16, False), (torch.bfloat16, 64, 16, True),
+                                              (torch.bfloat16, 32, 8, True)])
 @pytest.mark.parametrize("count,splits", [(1, 1), (40, 1), (1, 4)])
-def test_keys_that_stand_out_at_every_edge(dtype, d, page, count, splits):
+def test_keys_that_stand_out_at_every_edge(dtype, d, page, mma, count, splits):
     """Random keys score about 0.  One key at a time is made to score high in head 1 for the LAST token of a request of
     333 tokens (decoded alone, or the end of a portion of 40).  Head 0 listens to head 1 alone (``talk``), so it must
     bring that key's value where the window lets the token see it, and must not where it does not."""
@@ -235,7 +267,7 @@ def test_keys_that_stand_out_at_every_edge(dtype, d, page, count, splits):
         st.v[0][j, 0] = torch.full((d,), 7.0).to(dtype)                # head 0 reads its own key/value head's value there
         qmul = torch.full((2,), 1.0 / float(qdir.norm()))
         sink = torch.tensor([0.5, -0.5])
-        got = st.run(w, qmul, talk, sink, False, splits=splits)
+        got = st.run(w, qmul, talk, sink, False, splits=splits, mma=mma)
         want = st.want(w, qmul, talk, sink, False)
         assert rel_err(got, want) < (1e-5 if dtype == torch.float32 else 2e-2), name
         row = got[count - 1, :d]
