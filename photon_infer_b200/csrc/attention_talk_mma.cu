@@ -23,6 +23,7 @@
 // (s_h = qmul[h] raw_h).  Cache planes [pages][G][page_size][d]; the value plane holds whatever talk_prep wrote there.
 #include "common.cuh"
 #include <math.h>
+#include <type_traits>
 
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
@@ -48,7 +49,7 @@ static_assert(TM_HPW * HEAD_DIM <= (TM_NW > 8 ? 128 : 256), "heads x head size t
 
 constexpr size_t tm_smem_bytes(int bn) {
   return (size_t)TALK_H * 16 * TM_LD * 2 + (size_t)2 * TALK_G * bn * TM_LD * 2 + (size_t)TALK_H * 16 * (bn + 8) * 4 +
-         (size_t)TALK_H * TM_HP * 4 + 32 * 4;
+         (size_t)TALK_H * TM_HP * 8 + 32 * 4;
 }
 constexpr int TM_BN = tm_smem_bytes(64) <= 226 * 1024 ? 64 : 32;          // keys per tile
 static_assert(tm_smem_bytes(TM_BN) <= 226 * 1024, "shared memory");
@@ -92,7 +93,7 @@ struct TalkMmaParams {
   const int* block_table; int max_pages;  // [S, max_pages]
   const int* cu_tokens;                   // [S + 1] first token of each request in the step
   const int* positions;                   // [T], ascending by one inside a request
-  int page_size, num_pages, window, splits, tiles_per_seq;
+  int page_size, page_shift, num_pages, window, splits, tiles_per_seq;   // page_shift: log2(page_size) or -1
   const float* qmul; const float* talk; const float* sink;
   const float* gate; long gate_stride;    // float rows of H numbers, or null
   float* part;                            // splits > 1: [T][splits][H][d + 2]
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
   bf16* Ks = Qs + TALK_H * 16 * TM_LD;                                     // [G][BN][LD]
   bf16* Vs = Ks + TALK_G * TM_BN * TM_LD;                                  // [G][BN][LD]
   float* Sb = reinterpret_cast<float*>(Vs + TALK_G * TM_BN * TM_LD);       // [H][16][SLD]
-  float* Tm = Sb + TALK_H * 16 * TM_SLD;                                   // [H][HP]: talk[h][g] * qmul[g]
+  float2* Tm = reinterpret_cast<float2*>(Sb + TALK_H * 16 * TM_SLD);       // [H][HP]: talk[h][g] * qmul[g], twice (packed multiply-adds)
   int* pos_s = reinterpret_cast<int*>(Tm + TALK_H * TM_HP);                // [16] position of each row, -1: no row
   int* lo_s = pos_s + 16;                                                  // [16] first key each row sees
   pdl_wait();
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
     const int h = i / TM_HP, g = i - h * TM_HP;
     float w = 0.f;
     if (g < TALK_H) w = (P.talk ? P.talk[h * TALK_H + g] : (h == g ? 1.f : 0.f)) * P.qmul[g];
-    Tm[i] = w;
+    Tm[i] = make_float2(w, w);
   }
   const int pos_first = P.positions[tfirst], pos_last = P.positions[tfirst + nrows - 1];
   const int key_lo = (P.window > 0 && pos_first - P.window + 1 > 0) ? pos_first - P.window + 1 : 0;
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
       bool valid = key >= key_lo && key <= pos_last;
       size_t src = 0;
       if (valid) {
-        const int pidx = key / P.page_size;
+        const int pidx = P.page_shift >= 0 ? (key >> P.page_shift) : key / P.page_size;
         const int page = table[pidx];
         if (page < 0 || page >= P.num_pages) {
           if (cc == 0 && g == 0) report_error(P.err, PHOTON_DEV_BAD_PAGE, tfirst, key, page);
@@ -232,22 +233,24 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
       for (int g = 0; g < TALK_H; ++g) raw[g] = *reinterpret_cast<const float2*>(cell + g * 16 * TM_SLD);
 #pragma unroll
       for (int h = 0; h < TALK_H; ++h) {
-        float ax = 0.f, ay = 0.f;
+        float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int g4 = 0; g4 < TM_HP; g4 += 4) {
-          const float4 w = *reinterpret_cast<const float4*>(Tm + h * TM_HP + g4);
-          ax = fmaf(w.x, raw[g4].x, ax); ay = fmaf(w.x, raw[g4].y, ay);
-          if (g4 + 1 < TALK_H) { ax = fmaf(w.y, raw[g4 + 1].x, ax); ay = fmaf(w.y, raw[g4 + 1].y, ay); }
-          if (g4 + 2 < TALK_H) { ax = fmaf(w.z, raw[g4 + 2].x, ax); ay = fmaf(w.z, raw[g4 + 2].y, ay); }
-          if (g4 + 3 < TALK_H) { ax = fmaf(w.w, raw[g4 + 3].x, ax); ay = fmaf(w.w, raw[g4 + 3].y, ay); }
+        for (int g2 = 0; g2 < TM_HP; g2 += 2) {
+          const float4 w = *reinterpret_cast<const float4*>(Tm + h * TM_HP + g2);      // (w_g, w_g, w_g+1, w_g+1)
+          if (g2 < TALK_H) acc = __ffma2_rn(make_float2(w.x, w.y), raw[g2], acc);
+          if (g2 + 1 < TALK_H) acc = __ffma2_rn(make_float2(w.z, w.w), raw[g2 + 1], acc);
         }
-        *reinterpret_cast<float2*>(cell + h * 16 * TM_SLD) = make_float2(ax, ay);
+        *reinterpret_cast<float2*>(cell + h * 16 * TM_SLD) = acc;
       }
     }
     tm_wait<1>();
     __syncthreads();                                   // mixed scores complete; this tile's values are in place
     // ---- 3. running softmax and P V of the warp's heads
     const int p0 = pos_s[r0], p1 = pos_s[r0 + 8], lo0 = lo_s[r0], lo1 = lo_s[r0 + 8];
+    // every row of the block sees every key of the tile: the comparisons are left out
+    const bool whole = nrows == 16 && key_base >= lo_s[15] && key_base + TM_BN - 1 <= pos_s[0];
+    auto phase3 = [&](auto masked) {
+    constexpr bool MASK = decltype(masked)::value;
 #pragma unroll
     for (int hh = 0; hh < TM_HPW; ++hh) {
       const int h = warp + hh * TM_NW;
@@ -260,10 +263,10 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
       for (int j = 0; j < TM_BN / 8; ++j) {
         const int key = key_base + j * 8 + c2;
         const float2 a = *reinterpret_cast<const float2*>(S0 + j * 8), b = *reinterpret_cast<const float2*>(S1 + j * 8);
-        if (key >= lo0 && key <= p0) mx0 = fmaxf(mx0, a.x);
-        if (key + 1 >= lo0 && key + 1 <= p0) mx0 = fmaxf(mx0, a.y);
-        if (key >= lo1 && key <= p1) mx1 = fmaxf(mx1, b.x);
-        if (key + 1 >= lo1 && key + 1 <= p1) mx1 = fmaxf(mx1, b.y);
+        if (!MASK || (key >= lo0 && key <= p0)) mx0 = fmaxf(mx0, a.x);
+        if (!MASK || (key + 1 >= lo0 && key + 1 <= p0)) mx0 = fmaxf(mx0, a.y);
+        if (!MASK || (key >= lo1 && key <= p1)) mx1 = fmaxf(mx1, b.x);
+        if (!MASK || (key + 1 >= lo1 && key + 1 <= p1)) mx1 = fmaxf(mx1, b.y);
       }
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -285,10 +288,10 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
           const int j = kk * 2 + jj;
           const int key = key_base + j * 8 + c2;
           const float2 a = *reinterpret_cast<const float2*>(S0 + j * 8), b = *reinterpret_cast<const float2*>(S1 + j * 8);
-          const float w00 = (key >= lo0 && key <= p0) ? tm_exp2(fmaf(a.x, TM_LOG2E, -sub0)) : 0.f;
-          const float w01 = (key + 1 >= lo0 && key + 1 <= p0) ? tm_exp2(fmaf(a.y, TM_LOG2E, -sub0)) : 0.f;
-          const float w10 = (key >= lo1 && key <= p1) ? tm_exp2(fmaf(b.x, TM_LOG2E, -sub1)) : 0.f;
-          const float w11 = (key + 1 >= lo1 && key + 1 <= p1) ? tm_exp2(fmaf(b.y, TM_LOG2E, -sub1)) : 0.f;
+          const float w00 = (!MASK || (key >= lo0 && key <= p0)) ? tm_exp2(fmaf(a.x, TM_LOG2E, -sub0)) : 0.f;
+          const float w01 = (!MASK || (key + 1 >= lo0 && key + 1 <= p0)) ? tm_exp2(fmaf(a.y, TM_LOG2E, -sub0)) : 0.f;
+          const float w10 = (!MASK || (key >= lo1 && key <= p1)) ? tm_exp2(fmaf(b.x, TM_LOG2E, -sub1)) : 0.f;
+          const float w11 = (!MASK || (key + 1 >= lo1 && key + 1 <= p1)) ? tm_exp2(fmaf(b.y, TM_LOG2E, -sub1)) : 0.f;
           sum0 += w00 + w01; sum1 += w10 + w11;
           pa[jj * 2] = tm_pack(w00, w01);
           pa[jj * 2 + 1] = tm_pack(w10, w11);
@@ -304,6 +307,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
       l[hh][0] = l[hh][0] * corr0 + sum0;              // per-lane partial sums; the quad is added up at the end
       l[hh][1] = l[hh][1] * corr1 + sum1;
     }
+    };
+    if (whole) phase3(std::false_type{}); else phase3(std::true_type{});
     __syncthreads();                                   // the scores and the value tile are free
     if (it + 1 < ntiles) load_plane(P.v_cache, Vs, key_base + TM_BN);
     tm_commit();
@@ -368,7 +373,10 @@ PHOTON_API int photon_talk_mma(const void* q, long q_stride, void* out, long out
   TalkMmaParams P;
   P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out; P.out_stride = out_stride;
   P.k_cache = (const bf16*)k_cache; P.v_cache = (const bf16*)v_cache; P.block_table = block_table; P.max_pages = max_pages;
-  P.cu_tokens = cu_tokens; P.positions = positions; P.page_size = page_size; P.num_pages = num_pages; P.window = window;
+  P.cu_tokens = cu_tokens; P.positions = positions; P.page_size = page_size; P.num_pages = num_pages;
+  P.page_shift = -1;
+  for (int b = 0; b < 31; ++b) if ((1 << b) == page_size) P.page_shift = b;
+  P.window = window;
   P.splits = splits; P.tiles_per_seq = (max_tokens + 15) / 16; P.qmul = qmul; P.talk = talk; P.sink = sink; P.gate = gate;
   P.gate_stride = gate_stride; P.part = part; P.err = err;
   const long blocks = (long)S * P.tiles_per_seq;

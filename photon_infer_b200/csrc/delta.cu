@@ -20,17 +20,19 @@
 #include <math.h>
 
 // ---------------------------------------------------------------- convolution, silu, unit vectors
-// One block per (token, segment); a segment is one q head, one k head (dim channels, made a unit vector) or one v head
-// (vdim channels).  The taps before the step's first token of the request come from the state.
+// One warp per (token, segment); a segment is one q head, one k head (dim channels, made a unit vector) or one v head
+// (vdim channels).  The taps before the step's first token of the request come from the state.  A lane keeps up to
+// HOLD results until the head's norm is known (heads up to 32 * HOLD wide; wider ones are scaled in a second pass).
 template <typename TI>
 __global__ void __launch_bounds__(128)
 delta_conv_kernel(const TI* __restrict__ x, long x_stride, const float* __restrict__ taps_w, int taps,
                   const int* __restrict__ token_seq, const int* __restrict__ cu_tokens, const int* __restrict__ state_slots,
                   const float* __restrict__ state, long state_stride, long conv_offset, int num_slots,
                   float* __restrict__ y, int Gq, int H, int dim, int vdim, int* err) {
-  __shared__ float red[32];
   pdl_wait();
-  const int t = blockIdx.y, seg = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.y, seg = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (seg >= 2 * Gq + H) return;
   const int C = 2 * Gq * dim + H * vdim;
   const bool unit = seg < 2 * Gq;
   const int width = unit ? dim : vdim;
@@ -39,12 +41,18 @@ delta_conv_kernel(const TI* __restrict__ x, long x_stride, const float* __restri
   const int p = t - cu_tokens[s];                     // index of the token among the request's tokens of this step
   int slot = state_slots[s];
   if (slot >= num_slots) {
-    if (threadIdx.x == 0 && seg == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t, slot, num_slots);
+    if (lane == 0 && seg == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t, slot, num_slots);
     slot = -1;
   }
   const float* old = slot >= 0 ? state + (size_t)slot * state_stride + conv_offset : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  constexpr int HOLD = 8;
+  const bool hold = unit && width <= HOLD * 32;
+  float kept[HOLD];
+#pragma unroll
+  for (int n = 0; n < HOLD; ++n) {
+    const int i = lane + n * 32;
+    if (i >= width) break;
     const int c = c0 + i;
     float a = 0.f;
     for (int j = 0; j < taps; ++j) {
@@ -55,13 +63,37 @@ delta_conv_kernel(const TI* __restrict__ x, long x_stride, const float* __restri
       a = fmaf(taps_w[(size_t)c * taps + j], xv, a);
     }
     a = a / (1.0f + expf(-a));
+    kept[n] = a;
+    if (!hold) y[(size_t)t * C + c] = a;
+    ss += a * a;
+  }
+  for (int i = lane + HOLD * 32; i < width; i += 32) {  // the rest of a very wide segment
+    const int c = c0 + i;
+    float a = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;
+      float xv;
+      if (back <= p) xv = to_f32(x[(size_t)(t - back) * x_stride + c]);
+      else xv = old ? old[(size_t)(taps - 1 - (back - p)) * C + c] : 0.f;
+      a = fmaf(taps_w[(size_t)c * taps + j], xv, a);
+    }
+    a = a / (1.0f + expf(-a));
     y[(size_t)t * C + c] = a;
     ss += a * a;
   }
   if (!unit) return;
-  ss = block_sum(ss, red);
+  ss = warp_sum(ss);
   const float inv = (seg < Gq ? rsqrtf((float)dim) : 1.0f) / sqrtf(ss + 1e-6f);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) y[(size_t)t * C + c0 + i] *= inv;
+  if (hold) {
+#pragma unroll
+    for (int n = 0; n < HOLD; ++n) {
+      const int i = lane + n * 32;
+      if (i < width) y[(size_t)t * C + c0 + i] = kept[n] * inv;
+    }
+    return;
+  }
+  __syncwarp();
+  for (int i = lane; i < width; i += 32) y[(size_t)t * C + c0 + i] *= inv;
 }
 
 // The last taps - 1 projected rows of every request, after this step: thread per (request, channel).
@@ -88,15 +120,22 @@ __global__ void delta_conv_state_kernel(const TI* __restrict__ x, long x_stride,
 // ---------------------------------------------------------------- the recurrence
 // The columns of a head's state never meet: column j needs k, q, the two per-head numbers and v_j alone.  So one block
 // owns `vcols` neighbouring columns of one (request, head), and the launcher cuts a head into as many groups of columns
-// as fill the GPU.  Thread jl * RP + r holds rows r * RPT .. of its column in registers; the RP partial sums of a column
+// as fill the GPU.  Thread jl * RP + r holds the rows (i * RP + r) * 4 .. + 3, i < RPT / 4, of its column in registers
+// (neighbouring lanes read neighbouring quads of k and q: no bank conflicts); the RP partial sums of a column
 // lie in neighbouring lanes and meet by shuffles, in an order that depends on (RPT, RP) alone, which the launcher
 // picks from dim alone: a column's arithmetic is the same chain however the head was cut and whatever else the
 // step holds.  The inputs of CH tokens are staged in shared memory (the next chunk's are fetched into registers while
 // the current one is computed), so the walk meets one barrier per chunk.
-#define DELTA_CH 8
+#define DELTA_CH 16
 #define DELTA_FETCH 4                                    // values of a token's row that a thread fetches
 
+// a token in shared memory: q [dimp], k [dimp], v [vcols, padded to 4], then g, beta and two spare numbers
 static inline int delta_tok_floats(int dimp, int vcols) { return 2 * dimp + ((vcols + 3) & ~3) + 4; }   // rows stay 16-byte aligned
+
+__device__ __forceinline__ void delta_cp4(float* dst, const float* src, bool valid) {
+  const int n = valid ? 4 : 0;                            // 0: the four bytes become zero, nothing is read
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n) : "memory");
+}
 
 template <int RPT, int RP>
 __global__ void __launch_bounds__(256)
@@ -108,7 +147,7 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
   extern __shared__ __align__(16) float sm[];
   pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y, cg = blockIdx.z;
-  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = cu_tokens[s], t1 = cu_tokens[s + 1];
   if (t1 <= t0) return;
   const int slot = state_slots[s];
@@ -122,15 +161,18 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
   const int j = cg * vcols + jl;                          // the thread's column of the head
   const bool active = jl < vcols && j < vdim;
   const int hq = h / (H / Gq);
-  const int row0 = r * RPT;
+  auto row_of = [&](int i) { return ((i >> 2) * RP + r) * 4 + (i & 3); };      // the state row in register i
   float* S = slot >= 0 ? state + (size_t)slot * state_stride + (size_t)h * dim * vdim : nullptr;
-  float st[RPT];
+  float2 st[RPT / 2];                                     // pairs of neighbouring rows: the arithmetic below is packed
 #pragma unroll
-  for (int i = 0; i < RPT; ++i) st[i] = (S != nullptr && active && row0 + i < dim) ? S[(size_t)(row0 + i) * vdim + j] : 0.f;
-  // a token in shared memory: q [dimp], k [dimp], v [vcols, padded to 4], g, beta; CH tokens a buffer, two buffers
+  for (int i = 0; i < RPT; ++i) {
+    const float v = (S != nullptr && active && row_of(i) < dim) ? S[(size_t)row_of(i) * vdim + j] : 0.f;
+    if (i & 1) st[i >> 1].y = v; else st[i >> 1].x = v;
+  }
   const int vpad = (vcols + 3) & ~3;
   const int per_tok = 2 * dimp + vpad + 4;
   const int buf_floats = DELTA_CH * per_tok;
+  float* kqs = sm + 2 * buf_floats + warp * DELTA_CH;     // k . q of the chunk's tokens, a copy per warp
   for (int i = tid; i < 2 * buf_floats; i += nthreads) sm[i] = 0.f;
   const float decay_rate = expf(a_log[h]), bias = dt_bias[h];
   // what this thread brings of every token: up to DELTA_FETCH numbers of q | k | the block's columns of v
@@ -146,90 +188,118 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
       src_col[n] = 2 * Gq * dim + h * vdim + cg * vcols + (w - 2 * dim); dst_at[n] = 2 * dimp + (w - 2 * dim);
     }
   }
-  float pre[DELTA_CH][DELTA_FETCH];
-  float pre_ab = 0.f;                                     // threads 0 .. 2 CH - 1: a token's decay or step size
-  auto fetch = [&](int c0) {
+  float pre_ab = 0.f;                                     // threads 0 .. 2 CH - 1: a token's raw decay or step-size input
+  bool ab_live = false;
+  // the chunk that starts at token c0 travels into buffer `buf` (cp.async); the two per-head numbers come raw into a
+  // register and are turned into g and beta when they are stored, so that no thread waits for a load before the walk
+  auto fetch = [&](int c0, int buf) {
+    float* b = sm + buf * buf_floats;
 #pragma unroll
-    for (int tt = 0; tt < DELTA_CH; ++tt) {
-      const bool live = c0 + tt < t1;
-      const float* row = y + (size_t)(c0 + tt) * C;
+    for (int n = 0; n < DELTA_FETCH; ++n) {
+      if (src_col[n] < 0) continue;
+      const float* src = y + (size_t)c0 * C + src_col[n];
+      float* dst = b + dst_at[n];
 #pragma unroll
-      for (int n = 0; n < DELTA_FETCH; ++n) pre[tt][n] = (live && src_col[n] >= 0) ? row[src_col[n]] : 0.f;
+      for (int tt = 0; tt < DELTA_CH; ++tt) delta_cp4(dst + tt * per_tok, src + (size_t)tt * C, c0 + tt < t1);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     if (tid < 2 * DELTA_CH) {
-      const int t = c0 + (tid >> 1), which = tid & 1;
+      const int t = c0 + (tid >> 1);
+      pre_ab = 0.f; ab_live = t < t1;
+      if (ab_live) {
+        const size_t at = (size_t)t * ab_stride + ((tid & 1) == 0 ? h : H + h);
+        pre_ab = ab_dtype_bf16 ? __bfloat162float(((const bf16*)x_ab)[at]) : x_ab[at];
+      }
+    }
+  };
+  auto stash_ab = [&](int buf) {
+    if (tid < 2 * DELTA_CH) {
       float v = 0.f;
-      if (t < t1) {
-        // the two per-head numbers of the token: raw decay input, then raw beta input
-        const size_t at = (size_t)t * ab_stride + (which == 0 ? h : H + h);
-        const float raw = ab_dtype_bf16 ? __bfloat162float(((const bf16*)x_ab)[at]) : x_ab[at];
-        if (which == 0) {
-          const float z = raw + bias;
+      if (ab_live) {
+        if ((tid & 1) == 0) {
+          const float z = pre_ab + bias;
           const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));       // softplus
           v = expf(-decay_rate * sp);
         } else {
-          v = 1.0f / (1.0f + expf(-raw));
+          v = 1.0f / (1.0f + expf(-pre_ab));
         }
       }
-      pre_ab = v;
+      sm[buf * buf_floats + (tid >> 1) * per_tok + 2 * dimp + vpad + (tid & 1)] = v;
     }
-  };
-  auto stash = [&](int buf) {
-    float* b = sm + buf * buf_floats;
-#pragma unroll
-    for (int tt = 0; tt < DELTA_CH; ++tt) {
-#pragma unroll
-      for (int n = 0; n < DELTA_FETCH; ++n)
-        if (src_col[n] >= 0) b[tt * per_tok + dst_at[n]] = pre[tt][n];
-    }
-    if (tid < 2 * DELTA_CH) b[(tid >> 1) * per_tok + 2 * dimp + vpad + (tid & 1)] = pre_ab;
   };
   __syncthreads();
-  fetch(t0);
+  fetch(t0, 0);
   int buf = 0;
   for (int c0 = t0; c0 < t1; c0 += DELTA_CH, buf ^= 1) {
-    stash(buf);
-    __syncthreads();
-    if (c0 + DELTA_CH < t1) fetch(c0 + DELTA_CH);
+    stash_ab(buf);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                      // the chunk is in place, and the other buffer is read no more
+    if (c0 + DELTA_CH < t1) fetch(c0 + DELTA_CH, buf ^ 1);
     const float* b = sm + buf * buf_floats;
     const int n = min(DELTA_CH, t1 - c0);
+    if ((warp * 32) / RP >= vcols) continue;              // a warp without columns only helps to fetch
+    // k . q of every token of the chunk, once per warp: RP lanes a token, 32 / RP tokens a pass
+#pragma unroll
+    for (int tt0 = 0; tt0 < DELTA_CH; tt0 += 32 / RP) {
+      const float* tok = b + (tt0 + lane / RP) * per_tok;
+      const float4* q4 = reinterpret_cast<const float4*>(tok) + (lane % RP);
+      const float4* k4 = reinterpret_cast<const float4*>(tok + dimp) + (lane % RP);
+      float kq = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 kk = k4[i * RP], qq = q4[i * RP];
+        kq = fmaf(kk.x, qq.x, kq); kq = fmaf(kk.y, qq.y, kq); kq = fmaf(kk.z, qq.z, kq); kq = fmaf(kk.w, qq.w, kq);
+      }
+#pragma unroll
+      for (int o = RP / 2; o > 0; o >>= 1) kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      if (lane % RP == 0) kqs[tt0 + lane / RP] = kq;
+    }
+    __syncwarp();
     for (int tt = 0; tt < n; ++tt) {
       const float* tok = b + tt * per_tok;
-      const float4* q4 = reinterpret_cast<const float4*>(tok + row0);
-      const float4* k4 = reinterpret_cast<const float4*>(tok + dimp + row0);
+      const float4* q4 = reinterpret_cast<const float4*>(tok) + r;
+      const float4* k4 = reinterpret_cast<const float4*>(tok + dimp) + r;
       const float vj = active ? tok[2 * dimp + jl] : 0.f;
-      const float g = tok[2 * dimp + vpad], beta = tok[2 * dimp + vpad + 1];
-      float p1 = 0.f, p2 = 0.f, kq = 0.f;
+      const float2 gb = *reinterpret_cast<const float2*>(tok + 2 * dimp + vpad);
+      const float g = gb.x, beta = gb.y, kq = kqs[tt];
+      float4 kr[RPT / 4];
+      // packed sums over (even rows, odd rows), in up to four chains each so that a long column does not wait for itself
+      constexpr int NCH = RPT >= 32 ? 4 : (RPT >= 16 ? 2 : 1);
+      float2 p1[NCH], p2[NCH];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) { p1[c] = make_float2(0.f, 0.f); p2[c] = make_float2(0.f, 0.f); }
 #pragma unroll
       for (int i = 0; i < RPT / 4; ++i) {
-        const float4 kk = k4[i], qq = q4[i];
-        p1 = fmaf(st[4 * i], kk.x, p1);     p2 = fmaf(st[4 * i], qq.x, p2);     kq = fmaf(kk.x, qq.x, kq);
-        p1 = fmaf(st[4 * i + 1], kk.y, p1); p2 = fmaf(st[4 * i + 1], qq.y, p2); kq = fmaf(kk.y, qq.y, kq);
-        p1 = fmaf(st[4 * i + 2], kk.z, p1); p2 = fmaf(st[4 * i + 2], qq.z, p2); kq = fmaf(kk.z, qq.z, kq);
-        p1 = fmaf(st[4 * i + 3], kk.w, p1); p2 = fmaf(st[4 * i + 3], qq.w, p2); kq = fmaf(kk.w, qq.w, kq);
+        const float4 kk = k4[i * RP], qq = q4[i * RP];
+        kr[i] = kk;
+        p1[(2 * i) % NCH] = __ffma2_rn(st[2 * i], make_float2(kk.x, kk.y), p1[(2 * i) % NCH]);
+        p2[(2 * i) % NCH] = __ffma2_rn(st[2 * i], make_float2(qq.x, qq.y), p2[(2 * i) % NCH]);
+        p1[(2 * i + 1) % NCH] = __ffma2_rn(st[2 * i + 1], make_float2(kk.z, kk.w), p1[(2 * i + 1) % NCH]);
+        p2[(2 * i + 1) % NCH] = __ffma2_rn(st[2 * i + 1], make_float2(qq.z, qq.w), p2[(2 * i + 1) % NCH]);
       }
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) { s1 += p1[c].x + p1[c].y; s2 += p2[c].x + p2[c].y; }
 #pragma unroll
       for (int o = RP / 2; o > 0; o >>= 1) {
-        p1 += __shfl_xor_sync(0xffffffffu, p1, o);
-        p2 += __shfl_xor_sync(0xffffffffu, p2, o);
-        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
       }
-      const float u = beta * (vj - g * p1);
+      const float u = beta * (vj - g * s1);
+      const float2 uu = make_float2(u, u), gg = make_float2(g, g);
 #pragma unroll
       for (int i = 0; i < RPT / 4; ++i) {
-        const float4 kk = k4[i];
-        st[4 * i] = fmaf(g, st[4 * i], kk.x * u);
-        st[4 * i + 1] = fmaf(g, st[4 * i + 1], kk.y * u);
-        st[4 * i + 2] = fmaf(g, st[4 * i + 2], kk.z * u);
-        st[4 * i + 3] = fmaf(g, st[4 * i + 3], kk.w * u);
+        st[2 * i] = __ffma2_rn(gg, st[2 * i], __fmul2_rn(make_float2(kr[i].x, kr[i].y), uu));
+        st[2 * i + 1] = __ffma2_rn(gg, st[2 * i + 1], __fmul2_rn(make_float2(kr[i].z, kr[i].w), uu));
       }
-      if (active && r == 0) o_out[(size_t)(c0 + tt) * H * vdim + (size_t)h * vdim + j] = fmaf(g, p2, u * kq);
+      if (active && r == 0) o_out[(size_t)(c0 + tt) * H * vdim + (size_t)h * vdim + j] = fmaf(g, s2, u * kq);
     }
+    __syncwarp();                                         // kqs is rewritten in the next round
   }
   if (S != nullptr && active) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i)
-      if (row0 + i < dim) S[(size_t)(row0 + i) * vdim + j] = st[i];
+      if (row_of(i) < dim) S[(size_t)row_of(i) * vdim + j] = (i & 1) ? st[i >> 1].y : st[i >> 1].x;
   }
 }
 
@@ -265,7 +335,7 @@ PHOTON_API int photon_delta_conv(const void* x, long x_stride, int x_dtype, cons
   if (taps < 1 || Gq <= 0 || H <= 0 || H % Gq || dim <= 0 || vdim <= 0) return PHOTON_ERR_ARGUMENT;
   if (T > 65535 || S > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int C = 2 * Gq * dim + H * vdim;
-  dim3 grid(2 * Gq + H, T);
+  dim3 grid((2 * Gq + H + 3) / 4, T);
   int st;
   if (x_dtype == PHOTON_F32)
     st = launch_pdl(delta_conv_kernel<float>, grid, dim3(128), 0, stream, (const float*)x, x_stride, taps_w, taps, token_seq, cu_tokens,
@@ -297,6 +367,7 @@ static int delta_recurrent_launch(const float* y, const void* ab, long ab_stride
   if (groups < 1) groups = 1;
   int vcols = (vdim + groups - 1) / groups;
   vcols = ((vcols + 7) / 8) * 8;
+  if (vcols < 32 / RP) vcols = 32 / RP;                   // a full warp of columns
   if (vcols > most) vcols = most;
   if (vcols > vdim) vcols = vdim;
   groups = (vdim + vcols - 1) / vcols;
@@ -304,7 +375,7 @@ static int delta_recurrent_launch(const float* y, const void* ab, long ab_stride
   const int fetchers = (2 * dim + vcols + DELTA_FETCH - 1) / DELTA_FETCH;
   int threads = ((max(max(vcols * RP, fetchers), 2 * DELTA_CH) + 31) / 32) * 32;
   if (threads > 256 || groups > 65535) return PHOTON_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)2 * DELTA_CH * delta_tok_floats(RPT * RP, vcols) * sizeof(float);
+  const size_t smem = ((size_t)2 * DELTA_CH * delta_tok_floats(RPT * RP, vcols) + (size_t)(threads / 32) * DELTA_CH) * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_recurrent_kernel<RPT, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -326,11 +397,12 @@ PHOTON_API int photon_delta_recurrent(const float* y, const void* ab, long ab_st
   if (ab_dtype != PHOTON_F32 && ab_dtype != PHOTON_BF16) return PHOTON_ERR_ARGUMENT;
   if (S > 2147483647 / 2 || H > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int bf = ab_dtype == PHOTON_BF16;
-  // lanes per column (RP) and rows per lane (RPT, a multiple of 4) follow from dim alone
+  // lanes per column (RP) and rows per lane (RPT, a multiple of 4) follow from dim alone: few lanes a column, because
+  // every level of shuffles lengthens the chain from one token to the next
 #define DELTA_TRY(RPT, RP) if (dim <= RPT * RP) \
     return delta_recurrent_launch<RPT, RP>(y, ab, ab_stride, bf, a_log, dt_bias, cu_tokens, state_slots, state, state_stride, num_slots, \
                                            o, S, Gq, H, dim, vdim, err, stream)
-  DELTA_TRY(4, 4); DELTA_TRY(8, 4); DELTA_TRY(8, 8); DELTA_TRY(16, 8); DELTA_TRY(32, 8);
+  DELTA_TRY(4, 2); DELTA_TRY(4, 4); DELTA_TRY(8, 4); DELTA_TRY(16, 4); DELTA_TRY(32, 4); DELTA_TRY(64, 4);
   return PHOTON_ERR_UNSUPPORTED;
 }
 

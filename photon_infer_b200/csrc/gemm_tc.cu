@@ -164,8 +164,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int col0 = n0 + c;
           if (EPI == TC_EPI_F32) {
             float* dst = (float*)out + (size_t)row * ldo + col0;
+            if (col0 + 32 <= ncols && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (col0 + j < ncols) dst[j] = __uint_as_float(v[j]);
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (col0 + j < ncols) dst[j] = __uint_as_float(v[j]);
+            }
           } else {
             bf16* dst = (bf16*)out + (size_t)row * ldo + col0;
             float y[32];

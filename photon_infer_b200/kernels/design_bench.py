@@ -60,12 +60,15 @@ LEROSUN_WINDOW = 1024
 
 
 def lerosun_config(width: int, layers: int) -> dict:
-    """Alternating layers of attention with mixed heads (heads of 128, a window of 1,024 keys, half of a head rotated,
-    a sink, an output gate; the values are the keys) and of the gated delta rule (heads of 128 x 128, two value heads
-    per query/key head, convolutions of four taps); dense feed-forwards of 4 x width with a relu gate."""
-    heads, kv = width // 128, max(1, width // 1024)
+    """Alternating layers of attention with mixed heads (at most 16 heads of 128, since every head's score is a sum over
+    all heads and the tensor-core kernel keeps 16 tokens with all their heads in one block; a window of 1,024 keys, half
+    of a head rotated, a sink, an output gate; the values are the keys) and of the gated delta rule (heads of 128 x
+    128, two value heads per query/key head, convolutions of four taps); dense feed-forwards of 4 x width with a relu
+    gate."""
+    heads = width // 128
+    att_heads = min(16, heads)
     mlp = dict(kind="dense", ff=4 * width)
-    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5,
+    att = dict(type="attention", mixer=dict(heads=att_heads, kv_heads=max(1, att_heads // 8), dim=128, vdim=128, scale=128 ** -0.5,
                                             mask=dict(size=LEROSUN_WINDOW), rot=dict(base=10000.0, dims=64)), mlp=mlp)
     delta = dict(type="delta", mixer=dict(heads=heads, kv_heads=heads // 2, dim=128, vdim=128, conv=4), mlp=mlp)
     return dict(architecture="Lerosun", vocab=32000, width=width, norm=dict(eps=1e-5),

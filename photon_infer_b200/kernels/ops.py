@@ -1298,7 +1298,7 @@ def talk_mma_supported(n_q: int, n_kv: int, d: int) -> bool:
     heads_per_warp = -(-n_q // warps)
     if heads_per_warp * d > (128 if warps > 8 else 256):
         return False
-    smem = lambda bn: n_q * 16 * (d + 8) * 2 + 2 * n_kv * bn * (d + 8) * 2 + n_q * 16 * (bn + 8) * 4 + n_q * ((n_q + 3) & ~3) * 4 + 128
+    smem = lambda bn: n_q * 16 * (d + 8) * 2 + 2 * n_kv * bn * (d + 8) * 2 + n_q * 16 * (bn + 8) * 4 + n_q * ((n_q + 3) & ~3) * 8 + 128
     return smem(32) <= 226 * 1024
 
 
