@@ -294,7 +294,7 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
       }
       if (active && r == 0) o_out[(size_t)(c0 + tt) * H * vdim + (size_t)h * vdim + j] = fmaf(g, s2, u * kq);
     }
-    __syncwarp();                                         // kqs is rewritten in the next round
+    __syncwarp();                                         // kqs is rewritten for the next chunk
   }
   if (S != nullptr && active) {
 #pragma unroll
