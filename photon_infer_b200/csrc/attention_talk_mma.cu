@@ -15,8 +15,9 @@
 //      row i does not see are skipped;
 //   3. softmax and values: the warp that owns head h reads S_h back in the layout of an mma A operand, keeps a
 //      running maximum and sum per row in 32-bit, rounds the weights to bfloat16 and adds P V to its accumulators.
-// Keys stream from the paged cache by cp.async; the next tile's keys travel while phases 2 and 3 run, its values
-// while the next phases 1 and 2 run.  A token's key tiles may be shared out over `splits` blocks (decode steps): each
+// Keys and values stream from the paged cache by cp.async while phase 2 runs: the tile's values and the next tile's
+// keys.  Two block-wide barriers a tile (after phase 1 and after phase 2); phase 3 of a tile and phase 1 of the next
+// follow each other inside a warp, which owns the same heads in both.  A token's key tiles may be shared out over `splits` blocks (decode steps): each
 // leaves (maximum, sum, weighted sums) per head, merged in split order by photon_talk_merge (attention_talk.cu).
 //
 // Window: position i sees keys max(0, i - window + 1) .. i.  sink and gate may be null; talk null mixes nothing
@@ -175,8 +176,6 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
   }
   if (ntiles > 0) load_plane(P.k_cache, Ks, tile_begin * TM_BN);
   tm_commit();
-  if (ntiles > 0) load_plane(P.v_cache, Vs, tile_begin * TM_BN);
-  tm_commit();
 
   float m[TM_HPW][2], l[TM_HPW][2], o[TM_HPW][TM_ND][4];
 #pragma unroll
@@ -189,8 +188,10 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
 
   for (int it = 0; it < ntiles; ++it) {
     const int key_base = (tile_begin + it) * TM_BN;
-    tm_wait<1>();
-    __syncthreads();                                   // this tile's keys (and, the first time, Q, Tm, pos_s) are in place
+    if (it == 0) {
+      tm_wait<0>();
+      __syncthreads();                                 // Q, the first tile's keys, Tm and pos_s are in place
+    }
     // ---- 1. raw scores of the warp's heads
 #pragma unroll
     for (int hh = 0; hh < TM_HPW; ++hh) {
@@ -219,7 +220,9 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
         *reinterpret_cast<float2*>(S0 + 8 * TM_SLD + j * 8) = make_float2(s[j][2], s[j][3]);
       }
     }
-    __syncthreads();                                   // raw scores complete; the key tile is free
+    __syncthreads();                                   // raw scores complete; every warp has left the tile before: the
+                                                       // key tile and the value tile are free
+    load_plane(P.v_cache, Vs, key_base);
     if (it + 1 < ntiles) load_plane(P.k_cache, Ks, key_base + TM_BN);
     tm_commit();
     // ---- 2. the heads' scores are mixed, two neighbouring keys of one row per thread
@@ -243,8 +246,9 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
         *reinterpret_cast<float2*>(cell + h * 16 * TM_SLD) = acc;
       }
     }
-    tm_wait<1>();
-    __syncthreads();                                   // mixed scores complete; this tile's values are in place
+    tm_wait<0>();
+    __syncthreads();                                   // mixed scores complete; this tile's values and the next tile's keys
+                                                       // are in place
     // ---- 3. running softmax and P V of the warp's heads
     const int p0 = pos_s[r0], p1 = pos_s[r0 + 8], lo0 = lo_s[r0], lo1 = lo_s[r0 + 8];
     // every row of the block sees every key of the tile: the comparisons are left out
@@ -309,9 +313,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1) talk_mma_kernel(const TalkMmaPa
     }
     };
     if (whole) phase3(std::false_type{}); else phase3(std::true_type{});
-    __syncthreads();                                   // the scores and the value tile are free
-    if (it + 1 < ntiles) load_plane(P.v_cache, Vs, key_base + TM_BN);
-    tm_commit();
+    // no barrier here: a warp goes on to the raw scores of the next tile, which it writes into the rows of S that only
+    // it has just read; the next tile's first barrier keeps the mixing and the value tile behind the slowest warp
   }
   tm_wait<0>();
   pdl_launch_dependents();
