@@ -359,11 +359,13 @@ static int delta_recurrent_launch(const float* y, const void* ab, long ab_stride
                                   const float* dt_bias, const int* cu_tokens, const int* state_slots, float* state,
                                   long state_stride, int num_slots, float* o, int S, int Gq, int H, int dim, int vdim, int* err,
                                   cudaStream_t stream) {
-  // Columns a block owns: at most 256 / RP, and few enough that the step's blocks fill the GPU about twice; a multiple
-  // of 8 where the head has that many.  The cut changes no column's arithmetic.
+  // Columns a block owns: at most 256 / RP, and few enough that the step has about one block an SM: the warps of a
+  // block go to different schedulers of the SM, while the first warps of two blocks on one SM would share one, and a
+  // warp that walks tokens wants a scheduler to itself.  A multiple of 8 where the head has that many.  The cut
+  // changes no column's arithmetic.
   const int most = 256 / RP;
   const long heads = (long)S * H;
-  int groups = (int)((2L * photon_sm_count() + heads - 1) / heads);
+  int groups = (int)((photon_sm_count() + heads - 1) / heads);
   if (groups < 1) groups = 1;
   int vcols = (vdim + groups - 1) / groups;
   vcols = ((vcols + 7) / 8) * 8;
