@@ -127,7 +127,6 @@ __global__ void delta_conv_state_kernel(const TI* __restrict__ x, long x_stride,
 // step holds.  The inputs of CH tokens are staged in shared memory (the next chunk's are fetched into registers while
 // the current one is computed), so the walk meets one barrier per chunk.
 #define DELTA_CH 16
-#define DELTA_FETCH 4                                    // values of a token's row that a thread fetches
 
 // a token in shared memory: q [dimp], k [dimp], v [vcols, padded to 4], then g, beta and two spare numbers
 static inline int delta_tok_floats(int dimp, int vcols) { return 2 * dimp + ((vcols + 3) & ~3) + 4; }   // rows stay 16-byte aligned
@@ -138,7 +137,7 @@ __device__ __forceinline__ void delta_cp4(float* dst, const float* src, bool val
 }
 
 template <int RPT, int RP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(320)
 delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_stride, int ab_dtype_bf16,
                        const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                        const int* __restrict__ cu_tokens, const int* __restrict__ state_slots, float* __restrict__ state,
@@ -173,50 +172,46 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
   const int per_tok = 2 * dimp + vpad + 4;
   const int buf_floats = DELTA_CH * per_tok;
   float* kqs = sm + 2 * buf_floats + warp * DELTA_CH;     // k . q of the chunk's tokens, a copy per warp
+  float* obuf = sm + 2 * buf_floats + (nthreads >> 5) * DELTA_CH;     // the chunk's read-outs [CH][vpad], written out a chunk at a time
   for (int i = tid; i < 2 * buf_floats; i += nthreads) sm[i] = 0.f;
   const float decay_rate = expf(a_log[h]), bias = dt_bias[h];
-  // what this thread brings of every token: up to DELTA_FETCH numbers of q | k | the block's columns of v
+  // The warps behind the ones that own columns do nothing but fetch: every token's q | k | the block's columns of v.
+  const int nwork = (vcols * RP + 31) / 32;               // warps that walk
+  const int ftid = tid - nwork * 32, nfetch = nthreads - nwork * 32;
   const int rowlen = 2 * dim + vcols;
-  int src_col[DELTA_FETCH], dst_at[DELTA_FETCH];
-#pragma unroll
-  for (int n = 0; n < DELTA_FETCH; ++n) {
-    const int w = tid + n * nthreads;
-    src_col[n] = -1; dst_at[n] = 0;
-    if (w < dim) { src_col[n] = hq * dim + w; dst_at[n] = w; }
-    else if (w < 2 * dim) { src_col[n] = (Gq + hq) * dim + (w - dim); dst_at[n] = dimp + (w - dim); }
-    else if (w < rowlen && cg * vcols + (w - 2 * dim) < vdim) {
-      src_col[n] = 2 * Gq * dim + h * vdim + cg * vcols + (w - 2 * dim); dst_at[n] = 2 * dimp + (w - 2 * dim);
-    }
-  }
-  float pre_ab = 0.f;                                     // threads 0 .. 2 CH - 1: a token's raw decay or step-size input
+  float pre_ab = 0.f;                                     // fetch threads 0 .. 2 CH - 1: a token's raw decay or step-size input
   bool ab_live = false;
   // the chunk that starts at token c0 travels into buffer `buf` (cp.async); the two per-head numbers come raw into a
   // register and are turned into g and beta when they are stored, so that no thread waits for a load before the walk
   auto fetch = [&](int c0, int buf) {
+    if (ftid < 0) return;
     float* b = sm + buf * buf_floats;
-#pragma unroll
-    for (int n = 0; n < DELTA_FETCH; ++n) {
-      if (src_col[n] < 0) continue;
-      const float* src = y + (size_t)c0 * C + src_col[n];
-      float* dst = b + dst_at[n];
+    for (int w = ftid; w < rowlen; w += nfetch) {
+      int src_col, dst_at;
+      if (w < dim) { src_col = hq * dim + w; dst_at = w; }
+      else if (w < 2 * dim) { src_col = (Gq + hq) * dim + (w - dim); dst_at = dimp + (w - dim); }
+      else if (cg * vcols + (w - 2 * dim) < vdim) { src_col = 2 * Gq * dim + h * vdim + cg * vcols + (w - 2 * dim); dst_at = 2 * dimp + (w - 2 * dim); }
+      else continue;
+      const float* src = y + (size_t)c0 * C + src_col;
+      float* dst = b + dst_at;
 #pragma unroll
       for (int tt = 0; tt < DELTA_CH; ++tt) delta_cp4(dst + tt * per_tok, src + (size_t)tt * C, c0 + tt < t1);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    if (tid < 2 * DELTA_CH) {
-      const int t = c0 + (tid >> 1);
+    if (ftid < 2 * DELTA_CH) {
+      const int t = c0 + (ftid >> 1);
       pre_ab = 0.f; ab_live = t < t1;
       if (ab_live) {
-        const size_t at = (size_t)t * ab_stride + ((tid & 1) == 0 ? h : H + h);
+        const size_t at = (size_t)t * ab_stride + ((ftid & 1) == 0 ? h : H + h);
         pre_ab = ab_dtype_bf16 ? __bfloat162float(((const bf16*)x_ab)[at]) : x_ab[at];
       }
     }
   };
   auto stash_ab = [&](int buf) {
-    if (tid < 2 * DELTA_CH) {
+    if (ftid >= 0 && ftid < 2 * DELTA_CH) {
       float v = 0.f;
       if (ab_live) {
-        if ((tid & 1) == 0) {
+        if ((ftid & 1) == 0) {
           const float z = pre_ab + bias;
           const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));       // softplus
           v = expf(-decay_rate * sp);
@@ -224,7 +219,7 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
           v = 1.0f / (1.0f + expf(-pre_ab));
         }
       }
-      sm[buf * buf_floats + (tid >> 1) * per_tok + 2 * dimp + vpad + (tid & 1)] = v;
+      sm[buf * buf_floats + (ftid >> 1) * per_tok + 2 * dimp + vpad + (ftid & 1)] = v;
     }
   };
   __syncthreads();
@@ -237,7 +232,7 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
     if (c0 + DELTA_CH < t1) fetch(c0 + DELTA_CH, buf ^ 1);
     const float* b = sm + buf * buf_floats;
     const int n = min(DELTA_CH, t1 - c0);
-    if ((warp * 32) / RP >= vcols) continue;              // a warp without columns only helps to fetch
+    if (warp >= nwork) continue;                          // a fetching warp
     // k . q of every token of the chunk, once per warp: RP lanes a token, 32 / RP tokens a pass
 #pragma unroll
     for (int tt0 = 0; tt0 < DELTA_CH; tt0 += 32 / RP) {
@@ -292,7 +287,18 @@ delta_recurrent_kernel(const float* __restrict__ y, const float* x_ab, long ab_s
         st[2 * i] = __ffma2_rn(gg, st[2 * i], __fmul2_rn(make_float2(kr[i].x, kr[i].y), uu));
         st[2 * i + 1] = __ffma2_rn(gg, st[2 * i + 1], __fmul2_rn(make_float2(kr[i].z, kr[i].w), uu));
       }
-      if (active && r == 0) o_out[(size_t)(c0 + tt) * H * vdim + (size_t)h * vdim + j] = fmaf(g, s2, u * kq);
+      if (r == 0 && jl < vcols) obuf[tt * vpad + jl] = fmaf(g, s2, u * kq);
+    }
+    __syncwarp();
+    {
+      // the warp's columns of the chunk's read-outs go out together: 32 / RP neighbouring floats a token
+      constexpr int CPW = 32 / RP;
+      const int col0 = warp * CPW;
+      for (int idx = lane; idx < n * CPW; idx += 32) {
+        const int tt = idx / CPW, c = col0 + idx % CPW;
+        if (c < vcols && cg * vcols + c < vdim)
+          o_out[(size_t)(c0 + tt) * H * vdim + (size_t)h * vdim + cg * vcols + c] = obuf[tt * vpad + c];
+      }
     }
     __syncwarp();                                         // kqs is rewritten for the next chunk
   }
@@ -373,11 +379,11 @@ static int delta_recurrent_launch(const float* y, const void* ab, long ab_stride
   if (vcols > most) vcols = most;
   if (vcols > vdim) vcols = vdim;
   groups = (vdim + vcols - 1) / vcols;
-  // enough threads for the columns, and for fetching a token's row with at most DELTA_FETCH values a thread
-  const int fetchers = (2 * dim + vcols + DELTA_FETCH - 1) / DELTA_FETCH;
-  int threads = ((max(max(vcols * RP, fetchers), 2 * DELTA_CH) + 31) / 32) * 32;
-  if (threads > 256 || groups > 65535) return PHOTON_ERR_UNSUPPORTED;
-  const size_t smem = ((size_t)2 * DELTA_CH * delta_tok_floats(RPT * RP, vcols) + (size_t)(threads / 32) * DELTA_CH) * sizeof(float);
+  // the warps that own the columns, and two more that fetch
+  const int threads = ((vcols * RP + 31) / 32) * 32 + 64;
+  if (threads > 320 || groups > 65535) return PHOTON_ERR_UNSUPPORTED;
+  const size_t smem = ((size_t)2 * DELTA_CH * delta_tok_floats(RPT * RP, vcols) + (size_t)(threads / 32) * DELTA_CH +
+                       (size_t)DELTA_CH * ((vcols + 3) & ~3)) * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_recurrent_kernel<RPT, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
