@@ -65,4 +65,4 @@ def load_config(path: str):
 
 def _ensure_builtin() -> None:
     # importing the model module registers it
-    from ..models import fekopel, finelix, lerosun, llama  # noqa: F401
+    from ..models import fekopel, finelix, lerosun, llama, pebodra  # noqa: F401

@@ -29,7 +29,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(CSRC_DIR), "include")          # phot
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
-ALL_MODULES = ("elementwise", "rope_kv", "qk_norm", "attention", "latent", "gla", "delta", "attention_talk", "moe", "gemm_f32", "gemm_skinny", "gemm_skinny_fused",
+ALL_MODULES = ("elementwise", "rope_kv", "qk_norm", "attention", "latent", "gla", "delta", "attention_talk", "attention_diff", "linrec", "row_norms", "moe", "gemm_f32", "gemm_skinny", "gemm_skinny_fused",
                "gemm_skinny_static",
                "gemm_tc", "gemm_tc2", "sampling")
 

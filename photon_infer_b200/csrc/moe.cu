@@ -117,15 +117,21 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
       if (lane == 0) { ids[(size_t)t * top + j] = best; atomicAdd(&counts[best], 1); }
     }
     if (lane < top) weights[(size_t)t * top + lane] = mine / (sum + 1e-20f) * route_scale;
-  } else if (first && mode == 1) {
-    // scores: softmax over ALL experts.  Groups of E / n_groups neighbours: a group's score is its largest score,
-    // and only experts of the keep_groups best groups can be chosen.  Weights: the chosen scores over their sum,
-    // times route_scale.  Ties go to the lower index everywhere.
-    float mx = -INFINITY;
-    for (int e = 0; e < E; ++e) mx = fmaxf(mx, lg[e]);
-    float den = 0.f;
-    for (int e = 0; e < E; ++e) { const float p = expf(lg[e] - mx); lg[e] = p; den += p; }
-    for (int e = 0; e < E; ++e) lg[e] /= den;
+  } else if (first && (mode == 1 || mode == 2)) {
+    // mode 1: scores are the softmax over ALL experts; a group's score is its largest score; the weights are the chosen
+    // scores over their sum, times route_scale.  mode 2: scores are sigmoid(logit), each expert by itself; a group's
+    // score is the sum of its two largest scores; the weights are the chosen scores as they are, times route_scale.
+    // Groups of E / n_groups neighbours; only experts of the keep_groups best groups can be chosen.  Ties go to the
+    // lower index everywhere.
+    if (mode == 1) {
+      float mx = -INFINITY;
+      for (int e = 0; e < E; ++e) mx = fmaxf(mx, lg[e]);
+      float den = 0.f;
+      for (int e = 0; e < E; ++e) { const float p = expf(lg[e] - mx); lg[e] = p; den += p; }
+      for (int e = 0; e < E; ++e) lg[e] /= den;
+    } else {
+      for (int e = 0; e < E; ++e) lg[e] = 1.0f / (1.0f + expf(-lg[e]));
+    }
     if (n_groups > 1 && keep_groups < n_groups) {
       const int per = E / n_groups;
       float* kept = lg + E + 1;                          // n_groups flags behind the logits
@@ -135,8 +141,12 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
         float bs = -1.f;
         for (int g = 0; g < n_groups; ++g) {
           if (kept[g] != 0.f) continue;
-          float gs = -1.f;
-          for (int i = 0; i < per; ++i) gs = fmaxf(gs, lg[g * per + i]);
+          float gs = -1.f, second = -1.f;
+          for (int i = 0; i < per; ++i) {
+            const float v = lg[g * per + i];
+            if (v > gs) { second = gs; gs = v; } else if (v > second) second = v;
+          }
+          if (mode == 2 && per > 1) gs += second;
           if (gs > bs) { bs = gs; bg = g; }
         }
         kept[bg] = 1.f;
@@ -160,7 +170,10 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
       lg[best] = -2.f;
       atomicAdd(&counts[best], 1);
     }
-    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = weights[(size_t)t * top + j] / (sum + 1e-20f) * route_scale;
+    for (int j = 0; j < top; ++j) {
+      const float wj = weights[(size_t)t * top + j];
+      weights[(size_t)t * top + j] = mode == 1 ? wj / (sum + 1e-20f) * route_scale : wj * route_scale;
+    }
   }
   if (first && mode == 0) {
     float chosen_max = -INFINITY;
@@ -198,7 +211,9 @@ PHOTON_API int photon_moe_route(const void* h, long h_stride, int dtype, const v
 
 // mode 0: as above.  mode 1: scores are the softmax over all experts; with n_groups > 1 the experts form that many
 // equal groups of neighbours and only experts of the keep_groups groups with the largest best score can be chosen; the
-// weights are the chosen scores divided by their sum (+ 1e-20) times route_scale.  Wsg (may be null): one more row
+// weights are the chosen scores divided by their sum (+ 1e-20) times route_scale.  mode 2: scores are sigmoid(logit); a
+// group's score is the sum of its two largest scores; the weights are the chosen scores times route_scale, not divided
+// by their sum.  Wsg (may be null): one more row
 // [H] of the router's type; shared_gate [T] then gets sigmoid(Wsg . h), the gate of a shared expert.
 PHOTON_API int photon_moe_route_ex(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype,
                                    int T_, int H, int E, int top, int* ids, float* weights, int* counts, int mode,
@@ -206,9 +221,9 @@ PHOTON_API int photon_moe_route_ex(const void* h, long h_stride, int dtype, cons
                                    cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || H <= 0) return PHOTON_ERR_ARGUMENT;
-  if (mode != 0 && mode != 1) return PHOTON_ERR_ARGUMENT;
+  if (mode < 0 || mode > 2) return PHOTON_ERR_ARGUMENT;
   if (n_groups < 1 || keep_groups < 1 || keep_groups > n_groups || E % n_groups) return PHOTON_ERR_ARGUMENT;
-  if (mode == 1 && n_groups > 1 && (long)keep_groups * (E / n_groups) < top) return PHOTON_ERR_ARGUMENT;
+  if (mode != 0 && n_groups > 1 && (long)keep_groups * (E / n_groups) < top) return PHOTON_ERR_ARGUMENT;
   if ((Wsg == nullptr) != (shared_gate == nullptr)) return PHOTON_ERR_ARGUMENT;
   const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
   // few tokens (a decode step): one per block, so that every token's logits form on an SM of their own

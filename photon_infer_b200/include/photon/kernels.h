@@ -187,6 +187,60 @@ PHOTON_EXPORT int photon_delta_recurrent(const float* y, const void* ab, long ab
 PHOTON_EXPORT int photon_delta_out(const float* o, const void* z, long z_stride, int z_dtype, const float* norm_w, float eps,
                      void* out, long out_stride, int out_dtype, int T, int H, int vdim, cudaStream_t stream);
 
+/* ------------------------------------------------------------------ row_norms.cu: norms over parts of a row, PolyNorm, bounded values */
+/* The row x [T][H] (x_dtype, row stride x_stride) is cut into `groups` equal consecutive parts, each divided by its own
+ * sqrt(mean(part^2) + eps), the whole times w [H].  gate (float [T][H], row stride gate_stride): gate_mode 1 multiplies the
+ * row by silu(gate) before the norm, gate_mode 2 the normed row by sigmoid(gate); 0: no gate (null).  residual (float
+ * [T][H], may be null): the result is added to it in place and `out` (may then be null) receives the new rows of the
+ * stream; x null: `out` receives the stream's rows as they are.  Without a residual `out` receives the result. */
+PHOTON_EXPORT int photon_group_rmsnorm(const void* x, long x_stride, int x_dtype, const float* gate, long gate_stride, int gate_mode,
+                     float* residual, const void* w, int w_dtype, void* out, long out_stride, int out_dtype, int T, int H,
+                     int groups, float eps, cudaStream_t stream);
+/* out = a N(z) + b N(z^2) + c N(z^3) + e with N(u) = u / sqrt(mean(u^2) + eps) over the row; coef [4] = (a, b, c, e). */
+PHOTON_EXPORT int photon_polynorm(const void* z, long z_stride, int z_dtype, const void* coef, int coef_dtype, void* out,
+                     long out_stride, int out_dtype, int T, int F, float eps, cudaStream_t stream);
+/* x <- cap * tanh(x / cap) in place, `total` floats. */
+PHOTON_EXPORT int photon_softcap(float* x, long total, float cap, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ attention_diff.cu: two score maps per head over the same values */
+/* q [T][H * 2 * d], k [T][G * 2 * d] (head by head: map 1, map 2), v [T][G * dv] of in_dtype.  Biases (b_dtype, may be null) are
+ * added; every (head, map) of q and k is divided by its root mean square (eps inside the root) and multiplied by q_w / k_w [d]
+ * (w_dtype, may be null); its first rot_dims numbers are rotated (number j with j + rot_dims / 2, angle positions[t] *
+ * inv_freq[j]).  q_out [T][H * 2 * d] of out_dtype; keys go to k_cache [pages][G][page_size][2 d], values to v_cache
+ * [pages][G][page_size][dv] at slot_mapping[t] (-1: nothing).  Null caches: queries only. */
+PHOTON_EXPORT int photon_diff_prep(const void* q, long q_stride, const void* k, long k_stride, const void* v, long v_stride,
+                     int in_dtype, void* q_out, long qo_stride, int out_dtype, const void* q_b, const void* k_b, const void* v_b,
+                     int b_dtype, const void* q_w, const void* k_w, int w_dtype, float eps, const int* positions,
+                     const double* inv_freq, int rot_dims, const int* slot_mapping, void* k_cache, void* v_cache, int T, int H,
+                     int G, int d, int dv, int page_size, long num_slots, int* err, cudaStream_t stream);
+/* Per head: a_m = softmax_j((q_m . k_m) * scale) v over the keys the token sees, m = 1, 2; o = a_1 - lambda a_2;
+ * out = o / sqrt(mean(o^2) + eps) * out_scale.  out [T][n_q * dv]. */
+PHOTON_EXPORT int photon_diff_attention(const void* q, long q_stride, void* out, long out_stride, int dtype, const void* k_cache,
+                     const void* v_cache, const int* block_table, int max_pages, const int* token_seq, const int* positions,
+                     int T_, int n_q, int n_kv, int d, int dv, int page_size, int num_pages, int window, float scale,
+                     float lambda, float out_scale, float eps, int* err, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ linrec.cu: recurrences with one decay per head and token */
+/* y float [T][C] = silu(bias + causal convolution over `taps` tokens per channel) of x [T][>= C] (x_dtype); taps_w float
+ * [C][taps], the last column weighs the current token; the taps before a request's first token of the step come from its
+ * state rows [taps - 1][C] at conv_offset of state [num_slots][state_stride] (slot -1: zeros). */
+PHOTON_EXPORT int photon_conv_silu(const void* x, long x_stride, int x_dtype, const float* taps_w, const float* bias, int taps,
+                     const int* token_seq, const int* cu_tokens, const int* state_slots, const float* state, long state_stride,
+                     long conv_offset, int num_slots, float* y, int T, int C, int* err, cudaStream_t stream);
+/* The last taps - 1 input rows of every request of the step become its state rows (slot -1: nothing is stored). */
+PHOTON_EXPORT int photon_conv_state(const void* x, long x_stride, int x_dtype, int taps, const int* cu_tokens,
+                     const int* state_slots, float* state, long state_stride, long conv_offset, int num_slots, int S, int C,
+                     cudaStream_t stream);
+/* S_t = keep_t S_(t-1) + take_t k_t v_t^T, o_t = S_t^T q_t per head (S [N][dv] in the request's state row).  mode 0: a
+ * state-space layer (keep = exp(-exp(A_log) dt), take = dt = softplus(ga + dt_bias), out = o + D v; p0, p1, p2 = A_log,
+ * dt_bias, D).  mode 1: a matrix memory with capped log gates and a running maximum (ga, gb the raw input and forget
+ * gates, p0, p1 their biases; out = o / (max(|n . q|, exp(-m)) + 1e-6); n [H][N] and m [H] follow S in the state row). */
+PHOTON_EXPORT int photon_linrec(int mode, const float* q, long q_stride, const float* k, long k_stride, const float* v,
+                     long v_stride, const float* ga, const float* gb, long g_stride, const float* p0, const float* p1,
+                     const float* p2, float cap, float q_scale, const int* cu_tokens, const int* state_slots, float* state,
+                     long state_stride, int num_slots, float* out, long out_stride, int S, int H, int qk_heads, int N, int dv,
+                     int* err, cudaStream_t stream);
+
 /* ------------------------------------------------------------------ attention_talk.cu: attention whose heads' scores are mixed */
 /* Bias (float, may be null) on q [T][H * d] and k [T][G * d] of in_dtype, rotation of the first rot_dims numbers of a head
  * (number j with j + rot_dims / 2, angle positions[t] * inv_freq[j]); q_out of out_dtype; the rotated key goes to k_cache, the
@@ -247,7 +301,8 @@ PHOTON_EXPORT int photon_gla_chunked(const void* q, const void* k, const void* v
 PHOTON_EXPORT int photon_moe_route(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype, int T_,
                      int H, int E, int top, int* ids, float* weights, int* counts, cudaStream_t stream);
 /* mode 1: softmax over all experts, groups of neighbours of which only the keep_groups best (by their largest score) may
- * be chosen from, weights = chosen scores / (their sum + 1e-20) * route_scale.  Wsg [H] (may be null): shared_gate [T] =
+ * be chosen from, weights = chosen scores / (their sum + 1e-20) * route_scale.  mode 2: scores are sigmoid(logit), a group's
+ * score is the sum of its two largest, weights = chosen scores * route_scale.  Wsg [H] (may be null): shared_gate [T] =
  * sigmoid(Wsg . h). */
 PHOTON_EXPORT int photon_moe_route_ex(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype, int T_,
                         int H, int E, int top, int* ids, float* weights, int* counts, int mode, int n_groups, int keep_groups,

@@ -1201,6 +1201,223 @@ def delta_out(o: torch.Tensor, z: torch.Tensor, norm_w: torch.Tensor, eps: float
              T, heads, vdim, _stream()), "delta_out")
 
 
+# ----------------------------------------------------------------------------- norms over parts of a row
+
+GATE_MODES = {None: 0, "silu_before": 1, "sigmoid_after": 2}
+
+
+def group_rmsnorm(x: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, groups: int,
+                  out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                  gate: Optional[torch.Tensor] = None, gate_mode: Optional[str] = None) -> None:
+    """RMS norm in ``groups`` equal consecutive parts of a row: every part of ``x [T, H]`` (a view with a row stride) is
+    divided by its own ``sqrt(mean(part^2) + eps)``, the whole times ``weight [H]``.  ``gate`` (float32 ``[T, H]`` view):
+    ``gate_mode`` ``silu_before`` multiplies the row by ``silu(gate)`` before the norm, ``sigmoid_after`` the normed row by
+    ``sigmoid(gate)``.  ``residual`` (contiguous float32 ``[T, H]``): the result is added to it in place, and ``out`` (may
+    then be None) receives the stream's new rows in its own type; with ``x`` None ``out`` just receives the stream's rows.
+    Without a residual ``out`` receives the result."""
+    _cuda(x, weight, out, residual, gate)
+    ref = x if x is not None else residual
+    if ref is None or (out is None and residual is None):
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "group_rmsnorm: nothing to read or nothing to write")
+    T, H = ref.shape
+    if x is not None and (x.stride(1) != 1 or weight is None or weight.numel() != H or not weight.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "group_rmsnorm: x [T, H] with unit column stride and weight [H]")
+    if residual is not None and (residual.dtype != torch.float32 or residual.shape != (T, H) or not residual.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "group_rmsnorm: the residual stream must be contiguous float32 [T, H]")
+    if out is not None and (out.shape != (T, H) or out.stride(1) != 1):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "group_rmsnorm: out must be [T, H]")
+    if groups <= 0 or H % groups:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"group_rmsnorm: {H} numbers do not split into {groups} equal parts")
+    if gate_mode not in GATE_MODES or (gate is None) != (gate_mode is None):
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "group_rmsnorm: a gate goes with a gate mode (silu_before, sigmoid_after)")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (T, H) or gate.stride(1) != 1):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "group_rmsnorm: the gate must be a float32 [T, H] view")
+    f = _fn("row_norms", "photon_group_rmsnorm",
+            [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int,
+             c_int, c_float, c_void_p])
+    _check(f(_ptr(x), x.stride(0) if x is not None else 0, _dtype_code(x) if x is not None else F32, _ptr(gate),
+             gate.stride(0) if gate is not None else 0, GATE_MODES[gate_mode], _ptr(residual), _ptr(weight),
+             _dtype_code(weight) if weight is not None else F32, _ptr(out), out.stride(0) if out is not None else 0,
+             _dtype_code(out) if out is not None else F32, T, H, int(groups), float(eps), _stream()), "group_rmsnorm")
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out = a N(z) + b N(z^2) + c N(z^3) + e`` per row, powers element by element, ``N(u) = u / sqrt(mean(u^2) + eps)``;
+    ``coef [4] = (a, b, c, e)``."""
+    _cuda(z, coef, out)
+    T, F = z.shape
+    if z.stride(1) != 1 or out.shape != (T, F) or out.stride(1) != 1 or coef.numel() != 4 or not coef.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "polynorm: z and out [T, F], coef [4]")
+    f = _fn("row_norms", "photon_polynorm", [c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int,
+                                             c_float, c_void_p])
+    _check(f(_ptr(z), z.stride(0), _dtype_code(z), _ptr(coef), _dtype_code(coef), _ptr(out), out.stride(0), _dtype_code(out),
+             T, F, float(eps), _stream()), "polynorm")
+
+
+def softcap_(x: torch.Tensor, cap: float) -> None:
+    """``x <- cap * tanh(x / cap)`` in place (contiguous float32)."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "softcap: x must be contiguous float32")
+    f = _fn("row_norms", "photon_softcap", [c_void_p, c_long, c_float, c_void_p])
+    _check(f(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+# ----------------------------------------------------------------------------- attention with two score maps per head
+
+def diff_prep(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_out: torch.Tensor,
+              q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor], v_bias: Optional[torch.Tensor],
+              q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float, positions: torch.Tensor,
+              inv_freq: Optional[torch.Tensor], rot_dims: int, slot_mapping: Optional[torch.Tensor],
+              k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int,
+              value_dim: int, err: Optional[torch.Tensor]) -> None:
+    """Biases, the per-(head, map) RMS norm with a shared weight ``[dim]``, and the rotation of the first ``rot_dims``
+    numbers for ``q [T, heads * 2 * dim]`` and ``k [T, kv_heads * 2 * dim]`` (views); queries into ``q_out``, keys into
+    ``k_cache [pages, kv_heads, page_size, 2 * dim]`` and ``v [T, kv_heads * value_dim]`` (plus bias) into ``v_cache
+    [pages, kv_heads, page_size, value_dim]``.  Caches None: queries only."""
+    _cuda(q, k, v, q_out, q_bias, k_bias, v_bias, q_weight, k_weight, positions, inv_freq, slot_mapping, k_cache, v_cache, err)
+    T = q.shape[0]
+    d, dv = dim, value_dim
+    if q.shape != (T, heads * 2 * d) or q.stride(1) != 1 or q_out.shape != q.shape or q_out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_prep: q and q_out must be [T, heads * 2 * dim]")
+    write = k_cache is not None
+    page_size, num_slots = 1, 0
+    if write:
+        if k is None or v is None or k.shape != (T, kv_heads * 2 * d) or v.shape != (T, kv_heads * dv) or k.stride(1) != 1 \
+                or v.stride(1) != 1 or k.dtype != q.dtype or v.dtype != q.dtype:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_prep: k [T, kv_heads * 2 * dim], v [T, kv_heads * value_dim]")
+        _int32(slot_mapping, "slot_mapping")
+        if k_cache.dim() != 4 or k_cache.shape[1] != kv_heads or k_cache.shape[3] != 2 * d or v_cache.shape[:3] != k_cache.shape[:3] \
+                or v_cache.shape[3] != dv or k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype \
+                or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH,
+                              "diff_prep: caches must be contiguous [pages, kv_heads, page_size, 2 * dim | value_dim]")
+        page_size = k_cache.shape[2]
+        num_slots = k_cache.shape[0] * page_size
+    _int32(positions, "positions")
+    if inv_freq is not None and (inv_freq.dtype != torch.float64 or inv_freq.numel() != rot_dims // 2 or rot_dims % 2 or rot_dims > d):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_prep: inv_freq must be float64 [rot_dims / 2], rot_dims even, <= dim")
+    biases = [b for b in (q_bias, k_bias, v_bias) if b is not None]
+    weights = [w for w in (q_weight, k_weight) if w is not None]
+    if any(b.dtype != biases[0].dtype or not b.is_contiguous() for b in biases) or \
+            any(w.dtype != weights[0].dtype or w.numel() != d or not w.is_contiguous() for w in weights):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_prep: biases of one dtype, norm weights [dim] of one dtype")
+    f = _fn("attention_diff", "photon_diff_prep",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_long, c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(k) if write else None, k.stride(0) if write else 0, _ptr(v) if write else None,
+             v.stride(0) if write else 0, _dtype_code(q), _ptr(q_out), q_out.stride(0), _dtype_code(q_out), _ptr(q_bias),
+             _ptr(k_bias) if write else None, _ptr(v_bias) if write else None, _dtype_code(biases[0]) if biases else F32,
+             _ptr(q_weight), _ptr(k_weight), _dtype_code(weights[0]) if weights else F32, float(eps), _ptr(positions),
+             _ptr(inv_freq) if rot_dims else None, int(rot_dims) if inv_freq is not None else 0,
+             _ptr(slot_mapping) if write else None, _ptr(k_cache), _ptr(v_cache), T, heads, kv_heads, d, dv, page_size, num_slots,
+             _ptr(err), _stream()), "diff_prep")
+
+
+def diff_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                   token_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, value_dim: int,
+                   window: Optional[int], scale: float, lam: float, out_scale: float, eps: float,
+                   err: Optional[torch.Tensor]) -> None:
+    """Differential attention, the general kernel.  ``q [T, heads * 2 * dim]`` (view), ``out [T, heads * value_dim]``; per
+    head two softmax maps over the keys ``max(0, p - window + 1) .. p`` share the values; ``o = a1 - lam * a2``, then
+    ``o / sqrt(mean(o^2) + eps) * out_scale`` per head."""
+    _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, err)
+    T = q.shape[0]
+    if q.shape[1] != heads * 2 * dim or q.stride(1) != 1 or out.shape != (T, heads * value_dim) or out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_attention: q must be [T, heads * 2 * dim], out [T, heads * value_dim]")
+    if q.dtype != out.dtype or q.dtype != k_cache.dtype or q.dtype != v_cache.dtype:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "diff_attention: q, out and the caches must share one dtype")
+    if k_cache.dim() != 4 or k_cache.shape[1] != kv_heads or k_cache.shape[3] != 2 * dim or v_cache.shape[3] != value_dim \
+            or v_cache.shape[:3] != k_cache.shape[:3] or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_attention: caches [pages, kv_heads, page_size, 2 * dim | value_dim]")
+    for name, t in (("block_table", block_table), ("token_seq", token_seq), ("positions", positions)):
+        _int32(t, name)
+    f = _fn("attention_diff", "photon_diff_attention",
+            [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _dtype_code(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(token_seq), _ptr(positions), T, heads, kv_heads, dim, value_dim, k_cache.shape[2],
+             k_cache.shape[0], int(window) if window else 0, float(scale), float(lam), float(out_scale), float(eps), _ptr(err),
+             _stream()), "diff_attention")
+
+
+# ----------------------------------------------------------------------------- recurrences with one decay per head and token
+
+def conv_silu(x: torch.Tensor, taps_w: torch.Tensor, bias: Optional[torch.Tensor], token_seq: torch.Tensor,
+              cu_tokens: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, conv_offset: int, y: torch.Tensor,
+              num_seqs: int, err: Optional[torch.Tensor]) -> None:
+    """``y = silu(bias + causal convolution per channel)`` of ``x [T, C]`` (a view), ``taps_w`` float32 ``[C, taps]`` (the last
+    column weighs the current token), ``y`` float32 ``[T, C]``.  The ``taps - 1`` rows before a request's first token of the
+    step come from its state row at ``conv_offset``; afterwards the state gets the request's last ``taps - 1`` input rows."""
+    _cuda(x, taps_w, bias, token_seq, cu_tokens, state_slots, state, y, err)
+    T, C = x.shape
+    taps = taps_w.shape[1]
+    if x.stride(1) != 1 or taps_w.shape != (C, taps) or taps_w.dtype != torch.float32 or not taps_w.is_contiguous() or \
+            (bias is not None and (bias.dtype != torch.float32 or bias.numel() != C or not bias.is_contiguous())):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"conv_silu: x [T, {C}], float32 taps [{C}, taps] and bias [{C}]")
+    if y.shape != (T, C) or y.dtype != torch.float32 or not y.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "conv_silu: y must be contiguous float32 [T, C]")
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < conv_offset + (taps - 1) * C:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "conv_silu: state must be contiguous float32 [slots, row] with room for the taps")
+    for t, what in ((token_seq, "token_seq"), (cu_tokens, "cu_tokens"), (state_slots, "state_slots")):
+        _int32(t, what)
+    f = _fn("linrec", "photon_conv_silu",
+            [c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_long, c_int,
+             c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _dtype_code(x), _ptr(taps_w), _ptr(bias), taps, _ptr(token_seq), _ptr(cu_tokens),
+             _ptr(state_slots), _ptr(state), state.stride(0), int(conv_offset), state.shape[0], _ptr(y), T, C, _ptr(err),
+             _stream()), "conv_silu")
+    if taps > 1:
+        g = _fn("linrec", "photon_conv_state",
+                [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_void_p])
+        _check(g(_ptr(x), x.stride(0), _dtype_code(x), taps, _ptr(cu_tokens), _ptr(state_slots), _ptr(state), state.stride(0),
+                 int(conv_offset), state.shape[0], int(num_seqs), C, _stream()), "conv_state")
+
+
+LINREC_MODES = {"state_space": 0, "matrix_memory": 1}
+
+
+def linrec(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate_a: torch.Tensor, gate_b: Optional[torch.Tensor],
+           p0: torch.Tensor, p1: torch.Tensor, p2: Optional[torch.Tensor], cap: float, q_scale: float, cu_tokens: torch.Tensor,
+           state_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, num_seqs: int, heads: int, qk_heads: int,
+           dim: int, vdim: int, err: Optional[torch.Tensor]) -> None:
+    """The recurrence ``S <- keep S + take k v^T, o = S^T q`` over the tokens of a step, per request and head, with the
+    state ``[heads, dim, vdim]`` (then, for ``matrix_memory``, ``n [heads, dim]`` and ``m [heads]``) at the start of the
+    request's float32 state row.  ``state_space``: ``gate_a`` = raw step sizes ``[T, heads]``, ``p0, p1, p2`` = ``A_log``,
+    ``dt_bias``, ``D``; the output is ``o + D v``.  ``matrix_memory``: ``gate_a, gate_b`` = raw input and forget gates, ``p0,
+    p1`` their biases, ``cap`` their bound; the output is ``o / (max(|n . q|, exp(-m)) + 1e-6)``.  All inputs float32 views
+    with unit column stride; ``out`` float32 ``[T, heads * vdim]``."""
+    _cuda(q, k, v, gate_a, gate_b, p0, p1, p2, cu_tokens, state_slots, state, out, err)
+    if mode not in LINREC_MODES:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"linrec: unknown mode {mode!r}")
+    T = q.shape[0]
+    for t, w, what in ((q, qk_heads * dim, "q"), (k, qk_heads * dim, "k"), (v, heads * vdim, "v"), (gate_a, heads, "gate_a"),
+                       (gate_b, heads, "gate_b"), (out, heads * vdim, "out")):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (T, w) or t.stride(1) != 1):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"linrec: {what} must be a float32 [T, {w}] view")
+    if gate_b is not None and gate_b.stride(0) != gate_a.stride(0):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "linrec: both gates must have one row stride")
+    if (mode == "matrix_memory") != (gate_b is not None):
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "linrec: the matrix memory has two gates, the state-space layer one")
+    for t, what in ((p0, "p0"), (p1, "p1"), (p2, "p2")):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous()):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"linrec: {what} must be float32 [heads]")
+    need = heads * dim * vdim + (heads * dim + heads if mode == "matrix_memory" else 0)
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < need:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "linrec: state must be contiguous float32 [slots, row]")
+    _int32(cu_tokens, "cu_tokens")
+    _int32(state_slots, "state_slots")
+    f = _fn("linrec", "photon_linrec",
+            [c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p,
+             c_float, c_float, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p])
+    _check(f(LINREC_MODES[mode], _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(gate_a), _ptr(gate_b),
+             gate_a.stride(0), _ptr(p0), _ptr(p1), _ptr(p2), float(cap), float(q_scale), _ptr(cu_tokens), _ptr(state_slots),
+             _ptr(state), state.stride(0), state.shape[0], _ptr(out), out.stride(0), int(num_seqs), heads, qk_heads, dim, vdim,
+             _ptr(err), _stream()), "linrec")
+
+
 # ----------------------------------------------------------------------------- attention whose heads' scores are mixed
 
 def talk_prep(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor],
@@ -1435,7 +1652,9 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
     logits win and the weights are the softmax over the chosen logits.  ``softmax_all``: scores are the softmax
     over all experts; the experts form ``groups`` equal groups of neighbours, a group's score is its largest
     score and only experts of the ``keep_groups`` best groups can be chosen; the weights are the chosen scores
-    over their sum (+ 1e-20) times ``route_scale``.  ``w_shared_gate [1, H]``: also returns ``sigmoid(w . h)``
+    over their sum (+ 1e-20) times ``route_scale``.  ``sigmoid``: scores are ``sigmoid(logit)``, a group's score is the
+    sum of its two largest scores, and the weights are the chosen scores times ``route_scale`` (not divided by their
+    sum).  ``w_shared_gate [1, H]``: also returns ``sigmoid(w . h)``
     per token.  Returns ``(ids int32 [T, top], weights float32 [T, top], counts int32 [E])`` or, with a gate,
     those and ``gate float32 [T]``."""
     _cuda(h, w_router, bias, w_shared_gate)
@@ -1465,7 +1684,7 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
     return ids, weights, counts
 
 
-ROUTER_SCORING = {"softmax_chosen": 0, "softmax_all": 1}
+ROUTER_SCORING = {"softmax_chosen": 0, "softmax_all": 1, "sigmoid": 2}
 
 
 def moe_align(ids: torch.Tensor, counts: torch.Tensor):

@@ -135,7 +135,7 @@ class CausalLM:
 
     def kernel_modules(self) -> List[object]:
         """What this model launches in this dtype: module names and (name, definitions) pairs."""
-        mods: List[object] = ["elementwise", "sampling"]
+        mods: List[object] = ["elementwise", "sampling"] + (["row_norms"] if self.spec.logit_softcap is not None else [])
         if self.dtype == torch.float32:
             mods.append("gemm_f32")
         for _, part in self._skeleton.named_parts():
@@ -190,4 +190,6 @@ class CausalLM:
         logits = ops.linear(y, self.head, out_dtype=torch.float32)
         if self.spec.logit_scale is not None:
             logits.mul_(self.spec.logit_scale)
+        if self.spec.logit_softcap is not None:
+            ops.softcap_(logits, self.spec.logit_softcap)
         return logits

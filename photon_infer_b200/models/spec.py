@@ -63,6 +63,8 @@ class ModelSpec:
     # logits by ``logit_scale`` after the head (architectures that scale either; None: untouched)
     embedding_scale: Optional[float] = None
     logit_scale: Optional[float] = None
+    # logits <- logit_softcap * tanh(logits / logit_softcap) after the head (None: unbounded)
+    logit_softcap: Optional[float] = None
     # a norm that the embedded rows pass before the first block (None: they enter the stream as they are)
     embedding_norm: Optional[PartSpec] = None
     # parts that work on the residual stream between layers, by name (see RunEntry.before)

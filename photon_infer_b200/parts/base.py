@@ -174,6 +174,18 @@ class Scaled:
         return self.tensor.to(torch.float32) * self.scale.to(torch.float32)
 
 
+@dataclasses.dataclass
+class Normed:
+    """A pending output that passes a norm before the sum: ``residual += norm(tensor)`` (a layer whose norms sit on
+    its sublayers' outputs).  A consumer that knows the kind does norm and sum in one kernel (``Norm.add_normed``)."""
+    tensor: torch.Tensor
+    norm: "Norm"
+
+    def materialize(self) -> torch.Tensor:
+        """The normed rows as a 32-bit tensor, for a consumer that cannot take the norm into its own kernel."""
+        return self.norm.forward(self.tensor, torch.float32)
+
+
 def delta_terms(delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]:
     """``(d1, d2, scale)``: what is pending on the stream as ``scale * d1 + d2`` (each may be None)."""
     if isinstance(delta, Scaled):
@@ -187,7 +199,7 @@ def delta_pair(delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
     parallel block (mixer and feed-forward), which are summed with each other first and then into the stream."""
     if delta is None:
         return None, None
-    if isinstance(delta, Scaled):
+    if isinstance(delta, (Scaled, Normed)):
         return delta.materialize(), None
     if isinstance(delta, (tuple, list)):
         parts = [d for d in delta if d is not None]
@@ -209,6 +221,15 @@ class Norm(Part):
         if d1 is not None:
             residual.add_(d1.to(residual.dtype) + d2.to(residual.dtype) if d2 is not None else d1.to(residual.dtype))
         return self.forward(residual, out_dtype)
+
+    def add_normed(self, x: Optional[torch.Tensor], residual: torch.Tensor, out_dtype: Optional[torch.dtype]):
+        """``residual += forward(x)`` in 32-bit, in place (``x`` None: nothing is added); returns the stream's new rows
+        in ``out_dtype`` (None: nothing is returned).  A norm that sits on a sublayer's output fuses the three."""
+        if x is not None:
+            residual.add_(self.forward(x, torch.float32))
+        if out_dtype is None:
+            return None
+        return residual if out_dtype == residual.dtype else residual.to(out_dtype)
 
     def add_forward_rows(self, delta, residual: torch.Tensor, rows: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """Same as ``add_forward`` for the listed rows only; returns ``[len(rows), H]``."""

@@ -67,5 +67,41 @@ class SwiGLUFeedForward(FeedForward):
         return project(act, self.w_down)
 
 
+class PolyNormFeedForward(FeedForward):
+    """``W_down act(W_up h)`` with the PolyNorm activation ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e``: powers element by
+    element, ``N`` divides a token's vector of ff values by its root mean square (``eps`` inside the root), and the four
+    numbers ``(a, b, c, e)`` are a tensor of the layer.  The up product keeps 32-bit rows, which the activation reads
+    (its three norms are 32-bit) and rounds once."""
+    kernel_modules = ("row_norms",)
+
+    def required_kernels(self, dtype):
+        return list(self.kernel_modules) + (["gemm_skinny", "gemm_tc", "gemm_tc2"] if dtype == torch.bfloat16 else [])
+
+    def __init__(self, hidden_size: int, intermediate_size: int, eps: float, names=("up", "down", "act")):
+        self.hidden_size, self.intermediate_size, self.eps = hidden_size, intermediate_size, float(eps)
+        self.names = tuple(names)
+        self.w_up = self.w_down = self.coef = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        u, d, a = self.names
+        return [TensorSpec(u, (I, H)), TensorSpec(d, (H, I)), TensorSpec(a, (4,), role="vector", init="norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        u, d, a = self.names
+        self.w_up, self.w_down = tensors[u].contiguous(), tensors[d].contiguous()
+        self.coef = tensors[a].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        z = project(h, self.w_up, out_dtype=torch.float32)
+        act = torch.empty(z.shape, dtype=h.dtype, device=h.device)
+        ops.polynorm(z, self.coef, self.eps, act)
+        return project(act, self.w_down, out_dtype=torch.float32)
+
+
 register_feed_forward("swiglu", SwiGLUFeedForward)
+register_feed_forward("polynorm", PolyNormFeedForward)
 register_feed_forward("gated", SwiGLUFeedForward)

@@ -19,6 +19,8 @@ the stack is ``[E, ff, H]``), and so is the shared expert.  ``router_bias`` Fals
 which only the ``keep_groups`` with the largest best score may be chosen from, and the weights are the chosen scores
 over their sum times ``route_scale``.  ``shared_gate``: the shared expert's output is multiplied by
 ``sigmoid(W_sg h)``, one number per token (``shared.sg [1, H]``), computed with the router's logits in 32-bit.
+``scoring`` ``sigmoid``: scores are ``sigmoid(logit)``, each expert by itself; a group's score is the sum of its two largest
+scores; the weights are the chosen scores times ``route_scale``, not divided by their sum.
 """
 from __future__ import annotations
 

@@ -9,7 +9,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from .base import ChannelScalePart, Norm, TensorSpec, delta_terms
+from .base import ChannelScalePart, Norm, Normed, TensorSpec, delta_pair, delta_terms
 from .registry import register_norm, register_scale
 
 
@@ -91,6 +91,65 @@ class LayerNorm(Norm):
         return out
 
 
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: the row is cut into ``groups`` equal consecutive parts, each is divided by its own
+    ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by the weight ``[size]``, in 32-bit.  As the norm of a
+    sublayer's output (``add_normed``) it also does the residual sum and hands back the stream's new rows in the run
+    type, all in one kernel; as a norm of the stream (``forward``, the model's last norm) it normalises the rows it is
+    given."""
+    kernel_modules = ("row_norms",)
+
+    def __init__(self, size: int, eps: float, groups: int = 1, weight_name: str = "weight"):
+        if groups <= 0 or size % groups:
+            raise ValueError(f"{size} numbers do not split into {groups} equal parts")
+        self.size, self.eps, self.groups, self.weight_name = size, float(eps), int(groups), weight_name
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.weight_name, (self.size,), role="vector", init="norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out=out)
+        return out
+
+    def add_normed(self, x, residual, out_dtype):
+        if x is None and (out_dtype is None or out_dtype == residual.dtype):
+            return residual if out_dtype is not None else None
+        # the 32-bit run reads the stream itself; the bfloat16 run gets a rounded copy from the same kernel
+        out = None if out_dtype in (None, residual.dtype) else torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out=out, residual=residual)
+        if out_dtype is None:
+            return None
+        return residual if out is None else out
+
+    def add_forward(self, delta, residual, out_dtype):
+        if isinstance(delta, Normed):
+            delta.norm.add_normed(delta.tensor, residual, None)
+        else:
+            d1, d2 = delta_pair(delta)
+            if d1 is not None:
+                residual.add_(d1.to(residual.dtype) + d2.to(residual.dtype) if d2 is not None else d1.to(residual.dtype))
+        return self.forward(residual, out_dtype)
+
+    def add_forward_rows(self, delta, residual, rows, out_dtype):
+        idx = rows.long()
+        r = residual.index_select(0, idx)
+        if isinstance(delta, Normed):
+            delta.norm.add_normed(delta.tensor.index_select(0, idx), r, None)
+        else:
+            d = [x.index_select(0, idx) for x in delta_pair(delta) if x is not None]
+            for x in d:
+                r.add_(x.to(r.dtype))
+        return self.forward(r, out_dtype)
+
+
 class ChannelScale(ChannelScalePart):
     """``y = s * x`` with a learned vector ``s [size]`` (layer scale).  The product is formed in 32-bit inside the
     norm kernel that adds the sublayer's output to the residual stream."""
@@ -112,3 +171,4 @@ class ChannelScale(ChannelScalePart):
 register_scale("channel_scale", ChannelScale)
 register_norm("rms_norm", RMSNorm)
 register_norm("layer_norm", LayerNorm)
+register_norm("group_rms_norm", GroupRMSNorm)

@@ -50,5 +50,5 @@ def create_part(table_name: str, kind: str, params: dict):
 
 
 def _ensure_builtin() -> None:
-    from . import (attention, block, delta_rule, gla, latent_attention, mlp, moe, norm, normed_attention, rope,  # noqa: F401
-                   stream, talking_attention)                                       # (each registers itself)
+    from . import (attention, block, delta_rule, diff_attention, gla, latent_attention, matrix_memory, mlp, moe,  # noqa: F401
+                   norm, normed_attention, rope, state_space, stream, talking_attention)                                       # (each registers itself)
