@@ -25,7 +25,9 @@ depth and feed-forward size, with each design's own kernels timed alone against 
 first keys, a sink or bounded scores and an output gate; plain experts behind a grouped router), beside a Llama
 decoder with the same window.  ``--design lerosun`` does it for the Lerosun decoder (attention whose heads' scores
 are mixed before the softmax, with a window, a sink and an output gate; layers of the gated delta rule; feed-forwards
-with a relu gate), beside a Llama decoder with the same window and the Finelix decoder.
+with a relu gate), beside a Llama decoder with the same window and the Finelix decoder.  ``--design pebodra`` does it for
+the Pebodra decoder (norms on the sublayers' outputs; differential attention, some layers reading another layer's keys
+and values; state-space and matrix-memory layers; PolyNorm and routed feed-forwards), beside the same two.
 
 ``--impl reference`` runs lumia431/photon_infer itself where it could be built (``baseline/``); else it
 prints an ``unavailable`` line.
@@ -376,7 +378,7 @@ def main() -> int:
     ap.add_argument("--layers-3b", type=int, default=0, help="fewer layers for the 3B workload (0: all 28)")
     ap.add_argument("--layers-8b", type=int, default=0, help="fewer layers for the 8B workload (0: all 32)")
     ap.add_argument("--batch-8b", type=int, default=8)
-    ap.add_argument("--design", default=None, choices=["finelix", "fekopel", "lerosun"],
+    ap.add_argument("--design", default=None, choices=["finelix", "fekopel", "lerosun", "pebodra"],
                     help="compare this design with a Llama decoder of equal size instead of running the headline")
     ap.add_argument("--design-sizes", default="2048,4096", help="widths to run with --design")
     args = ap.parse_args()

@@ -1,7 +1,8 @@
-"""Prefill and decode throughput of another design (the Finelix, the Fekopel or the Lerosun decoder) beside a Llama
-decoder of equal width, depth and feed-forward size (``python bench.py --design finelix|fekopel|lerosun``), with the
-parts of a layer timed alone against their rooflines.  The Lerosun decoder also runs beside the Finelix decoder, the
-other design with a recurrent mixer (a matrix of state per head) next to attention.
+"""Prefill and decode throughput of another design (the Finelix, the Fekopel, the Lerosun or the Pebodra decoder) beside
+a Llama decoder of equal width, depth and feed-forward size (``python bench.py --design finelix|fekopel|lerosun|pebodra``),
+with the parts of a layer timed alone against their rooflines.  The Lerosun and the Pebodra decoder also run beside the
+Finelix decoder, the other design with a recurrent mixer (a matrix of state per head) and routed experts next to
+attention.
 
 Random weights drawn on the device, synthetic token ids, bfloat16.  Per size:
 
@@ -73,6 +74,31 @@ def lerosun_config(width: int, layers: int) -> dict:
     delta = dict(type="delta", mixer=dict(heads=heads, kv_heads=heads // 2, dim=128, vdim=128, conv=4), mlp=mlp)
     return dict(architecture="Lerosun", vocab=32000, width=width, norm=dict(eps=1e-5),
                 layers=[delta if i % 2 == 0 else att for i in range(layers)], loop=None)
+
+
+PEBODRA_WINDOW = 1024
+
+
+def pebodra_config(width: int, layers: int) -> dict:
+    """Layers in the order matrix memory, differential attention, state-space, differential attention that reads the
+    keys and values of the attention layer before it.  Recurrent heads of 128 x 128 (state-space: four taps, one group of B
+    and C per eight heads); attention with two maps of 128 per head and values of 256, so that queries and outputs are as
+    wide as the model, four query heads per key/value head, a window of 1,024 keys, half of a map rotated.  Dense
+    feed-forwards of 4 x width (PolyNorm) alternate with 16 gated experts of width, 2 per token from the best 2 of 4
+    groups."""
+    heads = width // 128
+    att_heads = max(1, width // 256)
+    dense = dict(kind="dense", ff=4 * width)
+    moe = dict(kind="moe", expert=dict(ff=width), router=dict(experts=16, top=2, groups=dict(count=4, keep=2)))
+    att = lambda extra: dict(heads=att_heads, kv_heads=max(1, att_heads // 4), dim=128, vdim=256, scale=128 ** -0.5, diff=0.3,
+                             mask=dict(size=PEBODRA_WINDOW), rot=dict(base=10000.0, dims=64), **extra)
+    kinds = [lambda i: dict(type="mlstm", mixer=dict(heads=heads, dim=128, vdim=128, gate_cap=15.0), mlp=dense),
+             lambda i: dict(type="attention", mixer=att({}), mlp=moe),
+             lambda i: dict(type="mamba2", mixer=dict(heads=heads, vdim=128, state=128, groups=max(1, heads // 8), conv=4,
+                                                      norm_groups=max(1, heads // 8)), mlp=moe),
+             lambda i: dict(type="attention", mixer=att(dict(kv_from=i - 2)), mlp=dense)]
+    return dict(architecture="Pebodra", vocab=32000, width=width, norm=dict(eps=1e-6, groups=4), logit_softcap=30.0,
+                layers=[kinds[i % 4](i) for i in range(layers)])
 
 
 def llama_config(width: int, layers: int, window=None) -> dict:
@@ -147,9 +173,23 @@ def _mixer_numbers(m, kind: str, tokens: int, contexts) -> tuple:
         state = len(contexts) * (m.heads * m.dim * m.vdim + (m.taps - 1) * m.channels) * 4 * 2
         flops = tokens * (w // 2) * 2 + 7 * tokens * m.heads * m.dim * m.vdim
         return state, flops
+    if kind == "ssm":
+        # the state and the convolution's rows are read and written once a step; per token and state element: the decay, the
+        # write and the read-out
+        state = len(contexts) * (m.heads * m.state * m.vdim + (m.taps - 1) * m.channels) * 4 * 2
+        return state, tokens * (w // 2) * 2 + 5 * tokens * m.heads * m.state * m.vdim
+    if kind == "memory":
+        state = len(contexts) * (m.heads * m.dim * m.vdim + m.heads * m.dim + m.heads) * 4 * 2
+        return state, tokens * (w // 2) * 2 + 5 * tokens * m.heads * m.dim * (m.vdim + 1)
     reach = getattr(m, "window", None)
     reach = None if reach is None else reach + getattr(m, "keep_first", 0)
     seen_by = lambda p: p + 1 if reach is None else min(p + 1, reach)      # keys the token at position p reads
+    if kind == "diff":
+        # two maps per head: two score products over 128 numbers and two weighted sums of the same values
+        pairs = sum(sum(seen_by(p) for p in range(c)) for c in contexts) if tokens > len(contexts) else sum(seen_by(c - 1) for c in contexts)
+        held = sum(seen_by(c - 1) for c in contexts)
+        return held * m.n_kv * (2 * m.head_dim + m.value_dim) * 2, \
+            tokens * (w // 2) * 2 + 2 * m.n_q * (2 * m.head_dim + 2 * m.value_dim) * pairs
     if kind in ("attention", "normed", "talking"):
         pairs = sum(sum(seen_by(p) for p in range(c)) for c in contexts) if tokens > len(contexts) else sum(seen_by(c - 1) for c in contexts)
         held = sum(seen_by(c - 1) for c in contexts)
@@ -168,6 +208,9 @@ def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
     """The mixer and the feed-forward of the first layer of every kind, alone, in a prefill step and a decode step."""
     from ..parts.attention import PagedAttention
     from ..parts.delta_rule import GatedDeltaRule
+    from ..parts.diff_attention import DifferentialAttention
+    from ..parts.matrix_memory import MatrixMemoryMixer
+    from ..parts.state_space import StateSpaceMixer
     from ..parts.gla import GatedLinearAttention
     from ..parts.latent_attention import LatentAttention
     from ..parts.moe import MoEFeedForward
@@ -198,13 +241,18 @@ def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
             block = model.blocks[e.layer]
             m = block.mixer()
             kind = {GatedLinearAttention: "gla", LatentAttention: "latent", PagedAttention: "attention",
-                    NormedAttention: "normed", TalkingAttention: "talking", GatedDeltaRule: "delta"}.get(type(m))
+                    NormedAttention: "normed", TalkingAttention: "talking", GatedDeltaRule: "delta",
+                    DifferentialAttention: "diff", StateSpaceMixer: "ssm", MatrixMemoryMixer: "memory"}.get(type(m))
             if kind == "normed":                     # the two kinds of layer are timed apart
                 kind_name = "normed_gated" if m.output_gate else "normed_sink"
+            elif kind == "diff":                     # a layer that owns its keys and values, and one that reads another's
+                kind_name = "diff" if m.own_kv else "diff_reader"
             else:
                 kind_name = kind
             ff = block.parts().get("feed_forward")
             fkind = None if ff is None else ("moe" if isinstance(ff, MoEFeedForward) else "dense")
+            if fkind == "dense" and not hasattr(ff, "w_gate_up"):
+                fkind = "polynorm"
             lc = runner._layer_caches[i]
             if kind and (kind_name, phase) not in seen:
                 seen.add((kind_name, phase))
@@ -278,7 +326,7 @@ def run_design_comparison(design: str, args, hbm_peak: float, tf_peak: float, pe
     steps, warmup = max(8, min(args.steps, 64)), max(args.warmup, 3)
     layers = {2048: 8, 4096: 4}
     make, window = {"finelix": (finelix_config, None), "fekopel": (fekopel_config, FEKOPEL_WINDOW),
-                    "lerosun": (lerosun_config, LEROSUN_WINDOW)}[design]
+                    "lerosun": (lerosun_config, LEROSUN_WINDOW), "pebodra": (pebodra_config, PEBODRA_WINDOW)}[design]
     line = {"design": design, "dtype": args.dtype, "data": "synthetic", "peaks": peak_src,
             "workload": {"prefill_tokens": PREFILL, "decode_batch": BATCH, "decode_context": PROMPT, "steps": steps,
                          "warmup": warmup}, "sizes": {}}
@@ -286,7 +334,7 @@ def run_design_comparison(design: str, args, hbm_peak: float, tf_peak: float, pe
         n_layers = layers.get(width, 4)
         point = {"layers": n_layers}
         models = [(design, make(width, n_layers)), ("llama", llama_config(width, n_layers, window))]
-        if design == "lerosun":
+        if design in ("lerosun", "pebodra"):
             models.append(("finelix", finelix_config(width, n_layers)))
         for name, cfg in models:
             print(f"[bench] {name} width {width}, {n_layers} layers", file=sys.stderr, flush=True)

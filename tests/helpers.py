@@ -403,3 +403,107 @@ def lerosun_plain_logits(folder: str, ids: Sequence[int]) -> torch.Tensor:
         cfg, tensors = lerosun_plain_model(folder)
         _lerosun_cache[key] = lerosun_plain.forward(cfg, tensors, list(ids))
     return _lerosun_cache[key]
+
+
+# ----------------------------------------------------------------------------- Pebodra
+
+def _patt(heads, kv_heads, dim, vdim, scale, diff, size=None, rot=None, kv_from=None):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, diff=diff)
+    if size:
+        m["mask"] = dict(size=size)
+    if rot:
+        m["rot"] = dict(base=rot[0], dims=rot[1])
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _pssm(heads, vdim, state, groups, conv, norm_groups):
+    return dict(heads=heads, vdim=vdim, state=state, groups=groups, conv=conv, norm_groups=norm_groups)
+
+
+def _pmem(heads, dim, vdim, cap):
+    return dict(heads=heads, dim=dim, vdim=vdim, gate_cap=cap)
+
+
+def _pmoe(experts, top, ff, groups=None):
+    r = dict(experts=experts, top=top)
+    if groups:
+        r["groups"] = dict(count=groups[0], keep=groups[1])
+    return dict(kind="moe", expert=dict(ff=ff), router=r)
+
+
+# Tiny Pebodra configurations that differ in every size, in the order of the layers and in which optional pieces they
+# have.  Windows are short, so that prompts and decoded tokens alike pass their edges many times.
+TINY_PEBODRA: Dict[str, dict] = {
+    # attention first; a later layer reads its keys and values through a LONGER window; two of three router groups;
+    # values neither as wide as a key nor twice as wide; rotation of half a map
+    "pb_a": dict(
+        config=dict(architecture="Pebodra", vocab=150, width=64, norm=dict(eps=1e-5, groups=2), logit_softcap=20.0,
+                    layers=[dict(type="attention", mixer=_patt(4, 2, 16, 24, 0.3, 0.2, 40, (5000.0, 8)), mlp=_pmoe(6, 2, 32, (3, 2))),
+                            dict(type="mlstm", mixer=_pmem(2, 24, 16, 8.0), mlp=_dense(96)),
+                            dict(type="attention", mixer=_patt(4, 2, 16, 24, 0.25, 0.35, 56, (5000.0, 8), kv_from=0), mlp=None),
+                            dict(type="mamba2", mixer=_pssm(4, 8, 16, 2, 3, 4), mlp=_pmoe(4, 1, 48))]),
+        seed=41, init_std=0.1, norm_std=0.1, block_size=16),
+    # the state-space layer first; attention that sees every earlier key, without rotation, read by a layer with a
+    # window; one norm group; no bound on the logits; values as wide as a map's keys; pages of 8
+    "pb_b": dict(
+        config=dict(architecture="Pebodra", vocab=210, width=96, norm=dict(eps=1e-6, groups=1),
+                    layers=[dict(type="mamba2", mixer=_pssm(2, 24, 8, 1, 2, 1), mlp=_dense(40)),
+                            dict(type="attention", mixer=_patt(3, 1, 16, 16, 0.3, 0.5), mlp=_dense(56)),
+                            dict(type="mlstm", mixer=_pmem(4, 8, 8, 3.0), mlp=None),
+                            dict(type="attention", mixer=_patt(3, 1, 16, 16, 0.2, 0.1, 19, kv_from=1), mlp=_pmoe(8, 3, 24, (4, 3)))]),
+        seed=42, init_std=0.08, norm_std=0.15, block_size=8),
+    # sizes that are multiples of nothing; a window of three keys; router groups of one expert each; seven taps;
+    # as many state groups as heads
+    "pb_c": dict(
+        config=dict(architecture="Pebodra", vocab=77, width=50, norm=dict(eps=2e-5, groups=5), logit_softcap=7.5,
+                    layers=[dict(type="mlstm", mixer=_pmem(3, 9, 33, 15.0), mlp=_pmoe(5, 3, 14, (5, 3))),
+                            dict(type="attention", mixer=_patt(5, 5, 6, 10, 0.4, 0.0, 3, (50.0, 6)), mlp=_dense(30)),
+                            dict(type="mamba2", mixer=_pssm(3, 11, 7, 3, 7, 3), mlp=None)]),
+        seed=43, init_std=0.12, norm_std=0.05, block_size=16),
+    # heads of 64 and 128; a window longer than most requests; pages of 32; one head
+    "pb_d": dict(
+        config=dict(architecture="Pebodra", vocab=90, width=32, norm=dict(eps=1e-5, groups=2), logit_softcap=50.0,
+                    layers=[dict(type="attention", mixer=_patt(2, 1, 64, 128, 0.09, 0.3, 100, (300000.0, 64)), mlp=_dense(24)),
+                            dict(type="mamba2", mixer=_pssm(2, 64, 128, 1, 4, 2), mlp=_pmoe(2, 2, 16)),
+                            dict(type="mlstm", mixer=_pmem(1, 128, 128, 12.0), mlp=_dense(48))]),
+        seed=44, init_std=0.15, norm_std=0.1, block_size=16),
+    # two layers read the first one's keys and values, one of them without a window (so everything is kept); a
+    # convolution of one tap (no rows to carry); a small bound on the gates; groups of two experts, one kept
+    "pb_e": dict(
+        config=dict(architecture="Pebodra", vocab=131, width=48, norm=dict(eps=1e-5, groups=3),
+                    layers=[dict(type="attention", mixer=_patt(2, 2, 24, 40, 0.2, 0.4, 24, (777.0, 4)), mlp=_pmoe(4, 2, 20, (2, 1))),
+                            dict(type="attention", mixer=_patt(2, 2, 24, 40, 0.3, 0.25, None, (777.0, 4), kv_from=0), mlp=None),
+                            dict(type="mamba2", mixer=_pssm(6, 4, 12, 2, 1, 1), mlp=_dense(72)),
+                            dict(type="attention", mixer=_patt(2, 2, 24, 40, 0.15, 0.6, 8, (777.0, 4), kv_from=0), mlp=_dense(36)),
+                            dict(type="mlstm", mixer=_pmem(2, 40, 12, 1.5), mlp=None)]),
+        seed=45, init_std=0.1, norm_std=0.1, block_size=16),
+}
+
+
+def make_pebodra_folder(path: str, name: str, dtype: str = "bfloat16") -> str:
+    from photon_infer_b200.weights import write_random_model
+    t = TINY_PEBODRA[name]
+    write_random_model(path, t["config"], seed=t["seed"], init_std=t["init_std"], norm_std=t["norm_std"], dtype=dtype)
+    return path
+
+
+_pebodra_cache: Dict[tuple, torch.Tensor] = {}
+_pebodra_models: Dict[str, tuple] = {}
+
+
+def pebodra_plain_model(folder: str):
+    from plain import pebodra_plain
+    if folder not in _pebodra_models:
+        _pebodra_models[folder] = pebodra_plain.read_folder(folder)
+    return _pebodra_models[folder]
+
+
+def pebodra_plain_logits(folder: str, ids: Sequence[int]) -> torch.Tensor:
+    from plain import pebodra_plain
+    key = (folder, tuple(ids))
+    if key not in _pebodra_cache:
+        cfg, tensors = pebodra_plain_model(folder)
+        _pebodra_cache[key] = pebodra_plain.forward(cfg, tensors, list(ids))
+    return _pebodra_cache[key]

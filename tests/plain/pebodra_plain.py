@@ -77,27 +77,33 @@ def attention_keys_values(h, w, m, pos, eps):
     return k, v
 
 
-def differential_attention(h, w, m, pos, eps, kv):
-    """``kv``: (keys, values) as ``attention_keys_values`` gives them, of this layer or of the layer it reads."""
-    n = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    rot = m.get("rot") or {}
-    q = (h @ w["q"].T + w["q.b"]).reshape(n, H, 2, d)
-    q = rotate_first_dims(unit_rms(q, eps) * w["q.norm"], pos, rot.get("dims", 0), rot.get("base", 10000.0))
-    k, v = kv
-    ok = window_visible(n, (m.get("mask") or {}).get("size"))
-    lam = difference_weight(w, m["diff"])
+def difference_of_maps(q, k, v, ok, scale, lam, diff, eps):
+    """q [n, H, 2, d], k [L, G, 2, d], v [L, G, dv], ok [n, L] (who sees whom) -> [n, H * dv].  Each map is a softmax
+    attention of its own over the same values; a head's output is a_1 - lam a_2, divided by its root mean square, times
+    1 - diff."""
+    H, G = q.shape[1], k.shape[1]
     heads = []
     for hh in range(H):
         g = hh // (H // G)
         maps = []
         for mp in range(2):
-            s = (q[:, hh, mp, :] @ k[:, g, mp, :].T) * m["scale"]
-            p = torch.softmax(s.masked_fill(~ok, -math.inf), dim=-1)
-            maps.append(p @ v[:, g, :])
-        o = maps[0] - lam * maps[1]
-        heads.append(unit_rms(o, eps) * (1.0 - m["diff"]))
-    return torch.cat(heads, dim=-1) @ w["o"].T + w["o.b"]
+            s = (q[:, hh, mp, :] @ k[:, g, mp, :].T) * scale
+            maps.append(torch.softmax(s.masked_fill(~ok, -math.inf), dim=-1) @ v[:, g, :])
+        heads.append(unit_rms(maps[0] - lam * maps[1], eps) * (1.0 - diff))
+    return torch.cat(heads, dim=-1)
+
+
+def differential_attention(h, w, m, pos, eps, kv):
+    """``kv``: (keys, values) as ``attention_keys_values`` gives them, of this layer or of the layer it reads."""
+    n = h.shape[0]
+    H, d = m["heads"], m["dim"]
+    rot = m.get("rot") or {}
+    q = (h @ w["q"].T + w["q.b"]).reshape(n, H, 2, d)
+    q = rotate_first_dims(unit_rms(q, eps) * w["q.norm"], pos, rot.get("dims", 0), rot.get("base", 10000.0))
+    k, v = kv
+    ok = window_visible(n, (m.get("mask") or {}).get("size"))
+    o = difference_of_maps(q, k, v, ok, m["scale"], difference_weight(w, m["diff"]), m["diff"], eps)
+    return o @ w["o"].T + w["o.b"]
 
 
 # ----------------------------------------------------------------------------- state-space mixer
@@ -209,9 +215,13 @@ def route(h, w_router, r):
     return chosen, s.gather(1, chosen)
 
 
-def moe_ff(h, w, mlp):
+def moe_ff(h, w, mlp, chosen=None):
+    """``chosen [n, top]``: experts to use instead of the router's own choice (their weights are still their scores)."""
     r = mlp["router"]
-    chosen, weight = route(h, w["router"], r)
+    if chosen is None:
+        chosen, weight = route(h, w["router"], r)
+    else:
+        weight = torch.sigmoid(h @ w["router"].T).gather(1, chosen)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
         for c, wt in zip(chosen[t].tolist(), weight[t]):
@@ -226,9 +236,11 @@ def local(tensors, prefix):
     return {k[len(prefix):]: t64(v) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, ids, layers_out=None):
+def forward(cfg, tensors, ids, layers_out=None, forced=None):
     """Logits [n, vocab] (float64) of one sequence.  ``layers_out``: a list that receives the stream after every
-    layer."""
+    layer.  ``forced``: for every mixture-of-experts layer in order, the experts ``[n, top]`` to use instead of the
+    router's choice."""
+    forced = list(forced) if forced is not None else None
     eps, groups = cfg["norm"]["eps"], cfg["norm"]["groups"]
     pos = torch.arange(len(ids))
     x = t64(tensors["embed"])[torch.tensor(ids)]
@@ -248,7 +260,7 @@ def forward(cfg, tensors, ids, layers_out=None):
         mlp = l.get("mlp")
         if mlp is not None:
             wf = local(tensors, p + "mlp.")
-            d = dense_ff(x, wf, eps) if mlp["kind"] == "dense" else moe_ff(x, wf, mlp)
+            d = dense_ff(x, wf, eps) if mlp["kind"] == "dense" else moe_ff(x, wf, mlp, forced.pop(0) if forced else None)
             x = x + group_rms_norm(d, t64(tensors[p + "norm2"]), groups, eps)
         if layers_out is not None:
             layers_out.append(x.clone())
