@@ -183,7 +183,8 @@ def ensure_built(modules: Iterable[object]) -> None:
 DEFAULT_SPECIALISATIONS = (("attention_flash", {"HEAD_DIM": 64}), ("attention_tc", {"HEAD_DIM": 64}),
                            ("attention_decode", {"HEAD_DIM": 64}), ("attention_flash", {"HEAD_DIM": 128}),
                            ("attention_tc", {"HEAD_DIM": 128}), ("attention_decode", {"HEAD_DIM": 128}),
-                           ("attention_talk_mma", {"HEAD_DIM": 128, "TALK_H": 16, "TALK_G": 2}))
+                           ("attention_talk_mma", {"HEAD_DIM": 128, "TALK_H": 16, "TALK_G": 2}),
+                           ("attention_diff_mma", {"DIFF_D": 128, "DIFF_DV": 256}))
 
 
 def build_all(verbose: bool = False) -> None:

@@ -1342,6 +1342,43 @@ def diff_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
              _stream()), "diff_attention")
 
 
+def diff_mma_supported(dtype: torch.dtype, heads: int, kv_heads: int, dim: int, value_dim: int) -> bool:
+    """The tensor-core kernel takes bfloat16, sizes that are multiples of 16, at most 64 query heads per key/value head,
+    and what fits its shared memory (queries of 64 rows, two stages of 64 keys and values, the two maps' outputs)."""
+    if dtype != torch.bfloat16 or dim % 16 or value_dim % 16 or heads // kv_heads > 64:
+        return False
+    stages, fin = 2 * 64 * (2 * dim + value_dim) * 2, 2 * 64 * value_dim * 4
+    return 64 * 2 * dim * 2 + max(stages, fin) <= 220 * 1024 and value_dim <= 256
+
+
+def diff_attention_mma(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                       cu_tokens: torch.Tensor, positions: torch.Tensor, query_lens, heads: int, kv_heads: int, dim: int,
+                       value_dim: int, window: Optional[int], scale: float, lam: float, out_scale: float, eps: float,
+                       err: Optional[torch.Tensor]) -> None:
+    """``diff_attention`` on the tensor cores (bfloat16): a block owns the query heads of one key/value head for up to
+    ``64 / (heads / kv_heads)`` neighbouring tokens of a request.  ``query_lens``: the requests' token counts (host)."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, err)
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "diff_attention_mma: bfloat16 only")
+    if q.shape[1] != heads * 2 * dim or q.stride(1) != 1 or out.shape != (T, heads * value_dim) or out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_attention_mma: q must be [T, heads * 2 * dim], out [T, heads * value_dim]")
+    if k_cache.dim() != 4 or k_cache.shape[1] != kv_heads or k_cache.shape[3] != 2 * dim or v_cache.shape[3] != value_dim \
+            or v_cache.shape[:3] != k_cache.shape[:3] or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "diff_attention_mma: caches [pages, kv_heads, page_size, 2 * dim | value_dim]")
+    for name, t in (("block_table", block_table), ("cu_tokens", cu_tokens), ("positions", positions)):
+        _int32(t, name)
+    per_block = 64 // (heads // kv_heads)
+    tiles = sum(-(-int(n) // per_block) for n in query_lens)
+    f = _fn("attention_diff_mma", "photon_diff_mma",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_void_p, c_void_p], defines={"DIFF_D": dim, "DIFF_DV": value_dim})
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(cu_tokens), _ptr(positions), len(query_lens), tiles, heads, kv_heads, k_cache.shape[2], k_cache.shape[0],
+             int(window) if window else 0, float(scale), float(lam), float(out_scale), float(eps), _ptr(err), _stream()),
+           "diff_attention_mma")
+
+
 # ----------------------------------------------------------------------------- recurrences with one decay per head and token
 
 def conv_silu(x: torch.Tensor, taps_w: torch.Tensor, bias: Optional[torch.Tensor], token_seq: torch.Tensor,

@@ -24,6 +24,7 @@ same path.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -66,7 +67,13 @@ class DifferentialAttention(Mixer):
         return (q, self.n_kv * 2 * self.head_dim, self.n_kv * self.value_dim) if self.own_kv else (q, 0, 0)
 
     def required_kernels(self, dtype):
-        return list(self.kernel_modules) + (["gemm_skinny", "gemm_tc", "gemm_tc2"] if dtype == torch.bfloat16 else [])
+        mods = list(self.kernel_modules) + (["gemm_skinny", "gemm_tc", "gemm_tc2"] if dtype == torch.bfloat16 else [])
+        if self._mma_ok(dtype):
+            mods.append(("attention_diff_mma", {"DIFF_D": self.head_dim, "DIFF_DV": self.value_dim}))
+        return mods
+
+    def _mma_ok(self, dtype) -> bool:
+        return USE_DIFF_MMA and ops.diff_mma_supported(dtype, self.n_q, self.n_kv, self.head_dim, self.value_dim)
 
     def tensor_specs(self) -> List[TensorSpec]:
         n, H, d = self.names, self.hidden_size, self.head_dim
@@ -128,10 +135,20 @@ class DifferentialAttention(Mixer):
         return out
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        """bfloat16 with sizes that are multiples of 16: the tensor-core kernel, for prompt portions and decoded tokens
+        alike.  float32 and other sizes: the general kernel, whose sums depend on a token's position alone."""
         group = ctx.groups[cache.group]
+        if self._mma_ok(q.dtype) and q.stride(0) % 8 == 0 and ctx.host_query_lens:
+            ops.diff_attention_mma(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions, ctx.host_query_lens,
+                                   self.n_q, self.n_kv, self.head_dim, self.value_dim, self.window, self.scale, self.lam,
+                                   1.0 - self.diff, self.eps, ctx.error_flag)
+            return
         ops.diff_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions, self.n_q, self.n_kv,
                            self.head_dim, self.value_dim, self.window, self.scale, self.lam, 1.0 - self.diff, self.eps,
                            ctx.error_flag)
 
+
+#: The tensor-core kernel for bfloat16 (``PHOTON_DIFF_MMA=0``: the general kernel everywhere).
+USE_DIFF_MMA = os.environ.get("PHOTON_DIFF_MMA", "1") != "0"
 
 register_mixer("diff_attention", DifferentialAttention)

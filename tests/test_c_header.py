@@ -39,6 +39,7 @@ def test_c_program_links_against_the_libraries(tmp_path):
     libs = [compile_module(m) for m in ALL_MODULES]
     libs += [compile_module(m, {"HEAD_DIM": 64}) for m in ("attention_flash", "attention_tc", "attention_decode")]
     libs.append(compile_module("attention_talk_mma", {"HEAD_DIM": 64, "TALK_H": 4, "TALK_G": 2}))
+    libs.append(compile_module("attention_diff_mma", {"DIFF_D": 32, "DIFF_DV": 64}))
     names = _declared()
     src = tmp_path / "use_header.c"
     src.write_text(

@@ -207,7 +207,7 @@ class _Cached:
         self.v = [torch.randn(L, G, dv, generator=g).to(dtype) for L in lengths]
         self.q = [(std * torch.randn(n, H, 2, d, generator=g)).to(dtype) for n in counts]
 
-    def run(self, window, scale, lam, diff, eps=1e-5):
+    def run(self, window, scale, lam, diff, eps=1e-5, mma=False):
         from photon_infer_b200.kernels import ops
         H, G, d, dv = self.dims
         page = self.page
@@ -230,8 +230,16 @@ class _Cached:
         pos = [L - n + i for L, n in zip(self.lengths, self.counts) for i in range(n)]
         out = torch.empty(q.shape[0], H * dv, dtype=self.dtype, device=DEV)
         err = torch.zeros(4, dtype=torch.int32, device=DEV)
-        ops.diff_attention(q, out, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(tseq), i32(pos), H, G, d, dv, window, scale, lam,
-                           1.0 - diff, eps, err)
+        if mma:
+            assert ops.diff_mma_supported(self.dtype, H, G, d, dv)
+            cu = [0]
+            for n in self.counts:
+                cu.append(cu[-1] + n)
+            ops.diff_attention_mma(q, out, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(cu), i32(pos), self.counts, H, G, d, dv, window,
+                                   scale, lam, 1.0 - diff, eps, err)
+        else:
+            ops.diff_attention(q, out, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(tseq), i32(pos), H, G, d, dv, window, scale, lam,
+                               1.0 - diff, eps, err)
         assert err.cpu().tolist()[0] == 0
         want = []
         for s, (L, n) in enumerate(zip(self.lengths, self.counts)):
@@ -249,6 +257,32 @@ def test_attention_prompts_decoding_and_batches(dtype, H, G, d, dv, page, window
     c = _Cached(lengths, counts, H, G, d, dv, page, dtype, seed=H * d, std=0.7)
     got, want = c.run(window, d ** -0.5, 0.37, 0.2)
     assert rel_err(got, want) < (2e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("H,G,d,dv,page,window", [(4, 2, 16, 32, 16, 40), (3, 1, 48, 96, 8, None), (2, 2, 64, 128, 32, 100), (5, 5, 32, 16, 16, 3),
+                                                  (8, 1, 128, 128, 16, 136), (8, 2, 128, 256, 16, 70), (6, 2, 16, 48, 4, 33)])
+def test_attention_on_the_tensor_cores(H, G, d, dv, page, window):
+    lengths, counts = [150, 37, 64, 1, 200, 300], [150, 1, 20, 1, 2, 129]
+    c = _Cached(lengths, counts, H, G, d, dv, page, torch.bfloat16, seed=H * d + 1, std=0.7)
+    got, want = c.run(window, d ** -0.5, 0.37, 0.2, mma=True)
+    assert rel_err(got, want) < 2e-2
+    general, _ = c.run(window, d ** -0.5, 0.37, 0.2)
+    assert rel_err(got, general.double()) < 2e-2
+
+
+@pytest.mark.parametrize("which_map", [0, 1])
+@pytest.mark.parametrize("count", [1, 30, 100])
+def test_a_key_that_stands_out_at_every_edge_on_the_tensor_cores(which_map, count):
+    H, G, d, dv, page, window, L = 2, 1, 32, 16, 16, 48, 230
+    for place in (L - 1, L - 2, L - window, L - window - 1, L - window + 1, 0, 1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 181, 182, 183, 191, 192, 100):
+        c = _Cached([L], [count], H, G, d, dv, page, torch.bfloat16, seed=place + 1, std=0.05)
+        direction = torch.zeros(d)
+        direction[3] = 4.0
+        c.k[0][place, 0, which_map] = direction.bfloat16()
+        c.q[0][-1, :, which_map] = (3 * direction).bfloat16()
+        c.v[0][place] = 25.0
+        got, want = c.run(window, 1.0, 0.6, 0.1, mma=True)
+        assert rel_err(got, want) < 3e-2, place
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
