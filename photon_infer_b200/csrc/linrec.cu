@@ -116,17 +116,33 @@ PHOTON_API int photon_conv_state(const void* x, long x_stride, int x_dtype, int 
 
 // ---------------------------------------------------------------- the recurrence
 // A block owns LR_COLS neighbouring columns of one (request, head): 8 lanes share a column, lane i of them holding rows
-// i, i + 8, ... of it in registers (RPL rows a lane, N <= 8 RPL).  The step's tokens of the request come in chunks of
-// LR_CHUNK: their keys, queries, the block's share of their values and their gates are staged in shared memory (one warp
-// turns the raw gate inputs into keep and take, the running maximum in token order), then the walk over the chunk
-// needs no barrier: per token RPL multiply-adds for the update, RPL for the read-out and three shuffles.  In mode 1
-// the block's last column is the vector n (its value is 1), so every block knows n . q for its own columns.
+// i RPL .. i RPL + RPL - 1 of it in registers (RPL a multiple of 4, N <= 8 RPL).  The step's tokens of the request come in
+// chunks of LR_CHUNK: their keys, queries, the block's share of their values and their raw gates arrive by cp.async in
+// one of two stages of shared memory while the chunk before is walked; one warp turns the raw gates into keep and take
+// (the running maximum in token order); then the walk over the chunk needs no barrier and no shuffle: per token RPL
+// multiply-adds for the update and RPL for the read-out (operands fetched 16 bytes at a time); the eight lanes' shares of
+// a column's read-out meet when the chunk is written out.  In mode 1 the block's last column is the vector n (its value
+// is 1), so every block knows n . q for its own columns.
 #define LR_CHUNK 16
 #define LR_COLS 16
 #define LR_THREADS 128
 
 __device__ __forceinline__ float lr_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float lr_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ void lr_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void lr_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void lr_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int K> __device__ __forceinline__ void lr_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(K) : "memory"); }
+
+// Eight shares of one sum, added in a fixed order.
+__device__ __forceinline__ float lr_sum8(const float* p) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  return ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+}
 
 template <int MODE, int RPL>
 __global__ void __launch_bounds__(LR_THREADS)
@@ -135,11 +151,16 @@ linrec_kernel(const float* __restrict__ q, long q_stride, const float* __restric
               long g_stride, const float* __restrict__ p0, const float* __restrict__ p1, const float* __restrict__ p2,
               float cap, float q_scale, const int* __restrict__ cu_tokens, const int* __restrict__ state_slots,
               float* __restrict__ state, long state_stride, int num_slots, float* __restrict__ out, long out_stride,
-              int H, int qk_heads, int N, int dv, int* err) {
-  constexpr int NP = 8 * RPL;                          // rows with padding
+              int H, int qk_heads, int N, int dv, int vec, int* err) {
+  constexpr int NPS = 8 * (RPL + 4);                   // a staged row: 8 lanes' rows, each lane's share 16 bytes further on
   constexpr int REAL = MODE == 1 ? LR_COLS - 1 : LR_COLS;   // columns of S per block
-  __shared__ float ks[LR_CHUNK][NP], qs[LR_CHUNK][NP], vs[LR_CHUNK][LR_COLS], os[LR_CHUNK][LR_COLS];
-  __shared__ float keep_s[LR_CHUNK], take_s[LR_CHUNK], floor_s[LR_CHUNK], raw_a[LR_CHUNK], raw_b[LR_CHUNK];
+  extern __shared__ __align__(16) float lr_smem[];
+  float* ks = lr_smem;                                 // [2][CHUNK][NPS]
+  float* qs = ks + 2 * LR_CHUNK * NPS;                 // [2][CHUNK][NPS]
+  float* vs = qs + 2 * LR_CHUNK * NPS;                 // [2][CHUNK][COLS]
+  float* raw = vs + 2 * LR_CHUNK * LR_COLS;            // [2][2][CHUNK]: the raw gates
+  __shared__ __align__(16) float os[LR_CHUNK][LR_COLS][8];
+  __shared__ float keep_s[LR_CHUNK], take_s[LR_CHUNK], floor_s[LR_CHUNK];
   __shared__ float m_run;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane & 7;                            // this lane's place among the 8 lanes of its column
@@ -163,102 +184,146 @@ linrec_kernel(const float* __restrict__ q, long q_stride, const float* __restric
   float S[RPL];
 #pragma unroll
   for (int i = 0; i < RPL; ++i) {
-    const int r = sub + 8 * i;
+    const int r = sub * RPL + i;
     float x = 0.f;
     if (st && live && r < N) x = is_n ? n_h[r] : S_h[(size_t)r * dv + c];
     S[i] = x;
   }
   if (tid == 0) m_run = (MODE == 1 && m_h) ? *m_h : 0.f;
+  // what no copy writes stays as it is set here: rows beyond N, columns beyond the head, the value 1 of the n column
+  for (int i = tid; i < 2 * LR_CHUNK * NPS; i += LR_THREADS) { ks[i] = 0.f; qs[i] = 0.f; }
+  for (int i = tid; i < 2 * LR_CHUNK * LR_COLS; i += LR_THREADS) vs[i] = (MODE == 1 && (i % LR_COLS) == LR_COLS - 1) ? 1.f : 0.f;
+  for (int i = tid; i < 4 * LR_CHUNK; i += LR_THREADS) raw[i] = 0.f;
+  __syncthreads();
   const int t0 = cu_tokens[s], t1 = cu_tokens[s + 1];
   const float a_h = MODE == 0 ? expf(p0[h]) : 0.f;     // the head's decay rate
-  for (int base = t0; base < t1; base += LR_CHUNK) {
+
+  auto issue = [&](int base, int stage) {
     const int cnt = min(LR_CHUNK, t1 - base);
-    __syncthreads();                                   // the chunk before is written out; m_run is set
-    for (int i = tid; i < LR_CHUNK * NP; i += LR_THREADS) {
-      const int tt = i / NP, r = i - tt * NP;
-      float kv = 0.f, qv = 0.f;
-      if (tt < cnt && r < N) {
-        kv = k[(size_t)(base + tt) * k_stride + (size_t)hq * N + r];
-        qv = q[(size_t)(base + tt) * q_stride + (size_t)hq * N + r] * q_scale;
+    float* kd = ks + (size_t)stage * LR_CHUNK * NPS;
+    float* qd = qs + (size_t)stage * LR_CHUNK * NPS;
+    if (vec) {
+      const int per = N / 4;                           // 16-byte pieces of a row; a piece never straddles two lanes' shares
+      for (int i = tid; i < cnt * per; i += LR_THREADS) {
+        const int tt = i / per, r = (i - tt * per) * 4;
+        const int at = tt * NPS + r + (r / RPL) * 4;
+        lr_cp16(kd + at, k + (size_t)(base + tt) * k_stride + (size_t)hq * N + r);
+        lr_cp16(qd + at, q + (size_t)(base + tt) * q_stride + (size_t)hq * N + r);
       }
-      ks[tt][r] = kv;
-      qs[tt][r] = qv;
+    } else {
+      for (int i = tid; i < cnt * N; i += LR_THREADS) {
+        const int tt = i / N, r = i - tt * N;
+        const int at = tt * NPS + r + (r / RPL) * 4;
+        lr_cp4(kd + at, k + (size_t)(base + tt) * k_stride + (size_t)hq * N + r);
+        lr_cp4(qd + at, q + (size_t)(base + tt) * q_stride + (size_t)hq * N + r);
+      }
     }
-    for (int i = tid; i < LR_CHUNK * LR_COLS; i += LR_THREADS) {
-      const int tt = i / LR_COLS, cc = i - tt * LR_COLS;
-      float x = 0.f;
-      if (MODE == 1 && cc == LR_COLS - 1) x = 1.f;
-      else if (tt < cnt && cc < REAL && c0 + cc < dv) x = v[(size_t)(base + tt) * v_stride + (size_t)h * dv + c0 + cc];
-      vs[tt][cc] = x;
+    const int ncol = min(REAL, dv - c0);
+    float* vd = vs + (size_t)stage * LR_CHUNK * LR_COLS;
+    for (int i = tid; i < cnt * ncol; i += LR_THREADS) {
+      const int tt = i / ncol, cc = i - tt * ncol;
+      lr_cp4(vd + tt * LR_COLS + cc, v + (size_t)(base + tt) * v_stride + (size_t)h * dv + c0 + cc);
     }
-    if (tid < LR_CHUNK) {
-      float a = 0.f, b = 0.f;
+    float* rd = raw + (size_t)stage * 2 * LR_CHUNK;
+    if (tid < cnt) lr_cp4(rd + tid, ga + (size_t)(base + tid) * g_stride + h);
+    else if (MODE == 1 && tid >= 32 && tid < 32 + cnt) lr_cp4(rd + LR_CHUNK + tid - 32, gb + (size_t)(base + tid - 32) * g_stride + h);
+    lr_commit();
+  };
+
+  if (t0 < t1) issue(t0, 0);
+  int stage = 0;
+  for (int base = t0; base < t1; base += LR_CHUNK, stage ^= 1) {
+    const int cnt = min(LR_CHUNK, t1 - base);
+    __syncthreads();                                   // the chunk before is written out: the other stage is free
+    if (base + LR_CHUNK < t1) { issue(base + LR_CHUNK, stage ^ 1); lr_wait<1>(); } else lr_wait<0>();
+    __syncthreads();                                   // this chunk has landed for every thread
+    const float* kd = ks + (size_t)stage * LR_CHUNK * NPS;
+    const float* qd = qs + (size_t)stage * LR_CHUNK * NPS;
+    const float* vd = vs + (size_t)stage * LR_CHUNK * LR_COLS;
+    const float* rd = raw + (size_t)stage * 2 * LR_CHUNK;
+    if (MODE == 0) {
       if (tid < cnt) {
-        a = ga[(size_t)(base + tid) * g_stride + h];
-        if (MODE == 1) b = gb[(size_t)(base + tid) * g_stride + h];
-      }
-      if (MODE == 0) {
-        const float dt = lr_softplus(a + p1[h]);
+        const float dt = lr_softplus(rd[tid] + p1[h]);
         keep_s[tid] = expf(-a_h * dt);
         take_s[tid] = dt;
-      } else {
-        raw_a[tid] = cap * tanhf((a + p0[h]) / cap);                       // log input gate
-        raw_b[tid] = lr_logsigmoid(cap * tanhf((b + p1[h]) / cap));        // log forget gate
       }
-    }
-    if (MODE == 1) {
-      __syncthreads();
-      if (tid == 0) {
-        float m = m_run;
-        for (int tt = 0; tt < cnt; ++tt) {
-          const float fm = raw_b[tt] + m;
-          const float mn = fmaxf(fm, raw_a[tt]);
-          keep_s[tt] = expf(fm - mn);
-          take_s[tt] = expf(raw_a[tt] - mn);
-          floor_s[tt] = expf(-mn);
-          m = mn;
-        }
-        m_run = m;
+    } else if (warp == 0) {
+      float gi = 0.f, gf = 0.f;
+      if (lane < cnt) {
+        gi = cap * tanhf((rd[lane] + p0[h]) / cap);                          // log input gate
+        gf = lr_logsigmoid(cap * tanhf((rd[LR_CHUNK + lane] + p1[h]) / cap));  // log forget gate
       }
+      float m = m_run, fm_mine = 0.f, mn_mine = 0.f;
+      for (int tt = 0; tt < cnt; ++tt) {               // the running maximum, in token order (every lane walks it)
+        const float fi = __shfl_sync(0xffffffffu, gi, tt), ff = __shfl_sync(0xffffffffu, gf, tt);
+        const float fm = ff + m;
+        const float mn = fmaxf(fm, fi);
+        if (lane == tt) { fm_mine = fm; mn_mine = mn; }
+        m = mn;
+      }
+      if (lane < cnt) { keep_s[lane] = expf(fm_mine - mn_mine); take_s[lane] = expf(gi - mn_mine); floor_s[lane] = expf(-mn_mine); }
+      if (lane == 0) m_run = m;
     }
     __syncthreads();
+    const float* kl = kd + sub * (RPL + 4);
+    const float* ql = qd + sub * (RPL + 4);
+#pragma unroll 4
     for (int tt = 0; tt < cnt; ++tt) {
       const float keep = keep_s[tt];
-      const float w = take_s[tt] * vs[tt][col];
-      float a0 = 0.f, a1 = 0.f;
+      const float w = take_s[tt] * vd[tt * LR_COLS + col];
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < RPL; ++i) {
-        const int r = sub + 8 * i;
-        S[i] = fmaf(ks[tt][r], w, keep * S[i]);
-        if (i & 1) a1 = fmaf(S[i], qs[tt][r], a1); else a0 = fmaf(S[i], qs[tt][r], a0);
+      for (int j = 0; j < RPL / 4; ++j) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kl + tt * NPS + 4 * j);
+        const float4 q4 = *reinterpret_cast<const float4*>(ql + tt * NPS + 4 * j);
+        S[4 * j + 0] = fmaf(k4.x, w, keep * S[4 * j + 0]);
+        S[4 * j + 1] = fmaf(k4.y, w, keep * S[4 * j + 1]);
+        S[4 * j + 2] = fmaf(k4.z, w, keep * S[4 * j + 2]);
+        S[4 * j + 3] = fmaf(k4.w, w, keep * S[4 * j + 3]);
+        a0 = fmaf(S[4 * j + 0], q4.x, a0);
+        a1 = fmaf(S[4 * j + 1], q4.y, a1);
+        a2 = fmaf(S[4 * j + 2], q4.z, a2);
+        a3 = fmaf(S[4 * j + 3], q4.w, a3);
       }
-      float a = a0 + a1;
-      a += __shfl_xor_sync(0xffffffffu, a, 1);
-      a += __shfl_xor_sync(0xffffffffu, a, 2);
-      a += __shfl_xor_sync(0xffffffffu, a, 4);
-      if (sub == 0) os[tt][col] = a;
+      os[tt][col][sub] = (a0 + a1) + (a2 + a3);         // the eight lanes' shares of a column meet after the walk
     }
     __syncthreads();
     for (int i = tid; i < cnt * REAL; i += LR_THREADS) {
       const int tt = i / REAL, cc = i - tt * REAL;
       if (c0 + cc >= dv) continue;
-      float y = os[tt][cc];
-      if (MODE == 0) y = fmaf(p2[h], vs[tt][cc], y);
-      else y = y / (fmaxf(fabsf(os[tt][LR_COLS - 1]), floor_s[tt]) + 1e-6f);
+      float y = lr_sum8(os[tt][cc]) * q_scale;         // the queries' factor, taken out of the sums
+      if (MODE == 0) y = fmaf(p2[h], vd[tt * LR_COLS + cc], y);
+      else y = y / (fmaxf(fabsf(lr_sum8(os[tt][LR_COLS - 1]) * q_scale), floor_s[tt]) + 1e-6f);
       out[(size_t)(base + tt) * out_stride + (size_t)h * dv + c0 + cc] = y;
     }
   }
   if (st && live) {
     if (!is_n) {
 #pragma unroll
-      for (int i = 0; i < RPL; ++i) { const int r = sub + 8 * i; if (r < N) S_h[(size_t)r * dv + c] = S[i]; }
+      for (int i = 0; i < RPL; ++i) { const int r = sub * RPL + i; if (r < N) S_h[(size_t)r * dv + c] = S[i]; }
     } else if (blockIdx.x == 0) {
 #pragma unroll
-      for (int i = 0; i < RPL; ++i) { const int r = sub + 8 * i; if (r < N) n_h[r] = S[i]; }
+      for (int i = 0; i < RPL; ++i) { const int r = sub * RPL + i; if (r < N) n_h[r] = S[i]; }
     }
   }
   __syncthreads();
   if (MODE == 1 && m_h && tid == 0 && blockIdx.x == 0) *m_h = m_run;
+}
+
+template <int MODE, int RPL>
+static int linrec_go(dim3 grid, cudaStream_t stream, const float* q, long q_stride, const float* k, long k_stride, const float* v,
+                     long v_stride, const float* ga, const float* gb, long g_stride, const float* p0, const float* p1,
+                     const float* p2, float cap, float q_scale, const int* cu_tokens, const int* state_slots, float* state,
+                     long state_stride, int num_slots, float* out, long out_stride, int H, int qk_heads, int N, int dv, int vec,
+                     int* err) {
+  const size_t smem = ((size_t)4 * LR_CHUNK * 8 * (RPL + 4) + 2 * LR_CHUNK * LR_COLS + 4 * LR_CHUNK) * sizeof(float);
+  if (smem > 36 * 1024) {                              // with the 9 KB of static arrays this passes the default limit
+    cudaError_t e = cudaFuncSetAttribute(linrec_kernel<MODE, RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  linrec_kernel<MODE, RPL><<<grid, LR_THREADS, smem, stream>>>(q, q_stride, k, k_stride, v, v_stride, ga, gb, g_stride, p0, p1, p2, cap,
+      q_scale, cu_tokens, state_slots, state, state_stride, num_slots, out, out_stride, H, qk_heads, N, dv, vec, err);
+  return launch_status();
 }
 
 template <int MODE>
@@ -267,18 +332,17 @@ static int linrec_launch(int rpl, dim3 grid, cudaStream_t stream, const float* q
                          const float* p1, const float* p2, float cap, float q_scale, const int* cu_tokens,
                          const int* state_slots, float* state, long state_stride, int num_slots, float* out, long out_stride,
                          int H, int qk_heads, int N, int dv, int* err) {
-#define LR_GO(R) linrec_kernel<MODE, R><<<grid, LR_THREADS, 0, stream>>>(q, q_stride, k, k_stride, v, v_stride, ga, gb, g_stride, p0, p1, \
-      p2, cap, q_scale, cu_tokens, state_slots, state, state_stride, num_slots, out, out_stride, H, qk_heads, N, dv, err)
-  if (rpl <= 2) LR_GO(2);
-  else if (rpl <= 4) LR_GO(4);
-  else if (rpl <= 6) LR_GO(6);
-  else if (rpl <= 8) LR_GO(8);
-  else if (rpl <= 12) LR_GO(12);
-  else if (rpl <= 16) LR_GO(16);
-  else if (rpl <= 24) LR_GO(24);
-  else if (rpl <= 32) LR_GO(32);
-  else return PHOTON_ERR_UNSUPPORTED;
-  return launch_status();
+  // 16-byte copies of keys and queries when every row piece is aligned
+  const int vec = (N % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0) ? 1 : 0;
+#define LR_GO(R) return linrec_go<MODE, R>(grid, stream, q, q_stride, k, k_stride, v, v_stride, ga, gb, g_stride, p0, p1, p2, cap, q_scale, \
+      cu_tokens, state_slots, state, state_stride, num_slots, out, out_stride, H, qk_heads, N, dv, vec, err)
+  if (rpl <= 4) LR_GO(4);
+  if (rpl <= 8) LR_GO(8);
+  if (rpl <= 12) LR_GO(12);
+  if (rpl <= 16) LR_GO(16);
+  if (rpl <= 24) LR_GO(24);
+  if (rpl <= 32) LR_GO(32);
+  return PHOTON_ERR_UNSUPPORTED;
 }
 
 // q, k: float [T][qk_heads * N] views (row strides in elements); v float [T][H * dv]; ga, gb: float [T][H] views with row
