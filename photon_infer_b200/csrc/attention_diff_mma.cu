@@ -75,7 +75,8 @@ diff_mma_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ ou
   const int GH = n_q / n_kv;
   const int g = blockIdx.y;
   // which request and which of its token tiles this block owns
-  int s = 0, tile = blockIdx.x, t_first = 0, n_tok = 0;
+  // (the last tiles first: with a causal walk they are the longest, and the short ones fill the tail of the grid)
+  int s = 0, tile = gridDim.x - 1 - blockIdx.x, t_first = 0, n_tok = 0;
   for (; s < num_seqs; ++s) {
     t_first = cu_tokens[s];
     n_tok = cu_tokens[s + 1] - t_first;

@@ -58,6 +58,25 @@ group_rmsnorm_kernel(const TX* x, long x_stride, const float* gate, long gate_st
         if (o) o[c] = from_f32<TO>(y);
       }
     }
+  } else if (nwarp % groups == 0) {
+    // several warps per part: every warp sums its slice, the slices of a part meet in shared memory in a fixed order
+    const int wpg = nwarp / groups, g = warp / wpg, slice = warp - g * wpg;
+    const float* p = rn_stash + (size_t)g * gs;
+    float ss = 0.f;
+    for (int i = slice * 32 + lane; i < gs; i += wpg * 32) ss += p[i] * p[i];
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int j = 0; j < wpg; ++j) tot += red[g * wpg + j];
+    const float inv = 1.0f / sqrtf(tot / (float)gs + eps);
+    for (int i = slice * 32 + lane; i < gs; i += wpg * 32) {
+      const int c = g * gs + i;
+      float y = p[i] * inv * load_w(w, w_bf16, c);
+      if (gate_mode == 2) y *= rn_sigmoid(gr[c]);
+      if (res) { y += res[c]; res[c] = y; }
+      if (o) o[c] = from_f32<TO>(y);
+    }
   } else {
     for (int g = 0; g < groups; ++g) {
       const float* p = rn_stash + (size_t)g * gs;
