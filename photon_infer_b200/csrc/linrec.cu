@@ -342,6 +342,8 @@ static int linrec_launch(int rpl, dim3 grid, cudaStream_t stream, const float* q
   if (rpl <= 16) LR_GO(16);
   if (rpl <= 24) LR_GO(24);
   if (rpl <= 32) LR_GO(32);
+  if (rpl <= 48) LR_GO(48);
+  if (rpl <= 64) LR_GO(64);
   return PHOTON_ERR_UNSUPPORTED;
 }
 
@@ -359,7 +361,7 @@ PHOTON_API int photon_linrec(int mode, const float* q, long q_stride, const floa
   if (mode != 0 && mode != 1) return PHOTON_ERR_ARGUMENT;
   if (H <= 0 || qk_heads <= 0 || H % qk_heads || N <= 0 || dv <= 0) return PHOTON_ERR_ARGUMENT;
   if (mode == 1 && !(cap > 0.f)) return PHOTON_ERR_ARGUMENT;
-  if (N > 256 || H > 65535 || S > 65535) return PHOTON_ERR_UNSUPPORTED;
+  if (N > 512 || H > 65535 || S > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int rpl = (N + 7) / 8;
   const int real = mode == 1 ? LR_COLS - 1 : LR_COLS;
   dim3 grid((dv + real - 1) / real, H, S);

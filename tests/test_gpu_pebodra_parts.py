@@ -411,7 +411,8 @@ def _run_recurrence(mode, H, Gq, N, dv, lengths, cuts, seed, slots_total=3):
     return [torch.cat(x) for x in got], data, (p0.double(), p1.double(), p2.double())
 
 
-SHAPES = [(4, 2, 16, 8), (3, 3, 7, 11), (2, 1, 48, 48), (1, 1, 128, 40), (2, 2, 40, 15), (6, 2, 12, 4), (1, 1, 200, 17)]
+SHAPES = [(4, 2, 16, 8), (3, 3, 7, 11), (2, 1, 48, 48), (1, 1, 128, 40), (2, 2, 40, 15), (6, 2, 12, 4), (1, 1, 200, 17), (1, 1, 300, 9),
+          (1, 1, 512, 16)]
 
 
 @pytest.mark.parametrize("H,Gq,N,dv", SHAPES)
