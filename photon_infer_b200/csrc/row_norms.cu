@@ -23,7 +23,8 @@ __device__ __forceinline__ float rn_sigmoid(float z) { return 1.0f / (1.0f + exp
 template <typename TX, typename TO>
 __global__ void __launch_bounds__(RN_THREADS)
 group_rmsnorm_kernel(const TX* x, long x_stride, const float* gate, long gate_stride, int gate_mode, float* residual,
-                     const void* __restrict__ w, int w_bf16, TO* out, long out_stride, int H, int groups, float eps) {
+                     const void* __restrict__ w, int w_bf16, TO* out, long out_stride, int H, int groups, float eps,
+                     const void* __restrict__ x_bias, int xb_bf16) {
   __shared__ float red[32];
   extern __shared__ __align__(16) float rn_stash[];              // H floats: the row as it enters the norm
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = RN_THREADS / 32;
@@ -37,6 +38,7 @@ group_rmsnorm_kernel(const TX* x, long x_stride, const float* gate, long gate_st
   const float* gr = gate ? gate + (size_t)r * gate_stride : nullptr;
   for (int i = tid; i < H; i += RN_THREADS) {
     float v = to_f32(xr[i]);
+    if (x_bias) v += load_w(x_bias, xb_bf16, i);                  // the bias of the product that made x
     if (gate_mode == 1) { const float z = gr[i]; v *= z * rn_sigmoid(z); }
     rn_stash[i] = v;
   }
@@ -98,9 +100,11 @@ group_rmsnorm_kernel(const TX* x, long x_stride, const float* gate, long gate_st
 // x [T][H] of x_dtype with row stride x_stride (elements); null with a residual: the stream's rows are only copied out.
 // gate: float [T][H] with row stride gate_stride, needed when gate_mode is 1 or 2.  residual: float [T][H] contiguous
 // or null.  w [H] of w_dtype.  out [T][H] of out_dtype with row stride out_stride, may be null when a residual is given.
+// x_bias [H] of xb_dtype (may be null): added to every row of x first (the bias of the product that made x).
 PHOTON_API int photon_group_rmsnorm(const void* x, long x_stride, int x_dtype, const float* gate, long gate_stride,
                                     int gate_mode, float* residual, const void* w, int w_dtype, void* out, long out_stride,
-                                    int out_dtype, int T, int H, int groups, float eps, cudaStream_t stream) {
+                                    int out_dtype, int T, int H, int groups, float eps, const void* x_bias, int xb_dtype,
+                                    cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || groups <= 0 || H % groups || gate_mode < 0 || gate_mode > 2) return PHOTON_ERR_ARGUMENT;
   if ((gate_mode != 0) != (gate != nullptr)) return PHOTON_ERR_ARGUMENT;
@@ -114,7 +118,7 @@ PHOTON_API int photon_group_rmsnorm(const void* x, long x_stride, int x_dtype, c
     if (smem > 48 * 1024) { cudaError_t e_ = cudaFuncSetAttribute(group_rmsnorm_kernel<TX, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
                             if (e_ != cudaSuccess) return (int)e_; } \
     group_rmsnorm_kernel<TX, TO><<<T, RN_THREADS, smem, stream>>>((const TX*)x, x_stride, gate, gate_stride, gate_mode, residual, \
-        w, wb, (TO*)out, out_stride, H, groups, eps); \
+        w, wb, (TO*)out, out_stride, H, groups, eps, x_bias, xb_dtype == PHOTON_BF16); \
     return launch_status(); } while (0)
   if (x_dtype == PHOTON_F32 && out_dtype == PHOTON_F32) RN_GO(float, float);
   if (x_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16) RN_GO(float, bf16);

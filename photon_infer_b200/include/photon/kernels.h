@@ -195,7 +195,7 @@ PHOTON_EXPORT int photon_delta_out(const float* o, const void* z, long z_stride,
  * stream; x null: `out` receives the stream's rows as they are.  Without a residual `out` receives the result. */
 PHOTON_EXPORT int photon_group_rmsnorm(const void* x, long x_stride, int x_dtype, const float* gate, long gate_stride, int gate_mode,
                      float* residual, const void* w, int w_dtype, void* out, long out_stride, int out_dtype, int T, int H,
-                     int groups, float eps, cudaStream_t stream);
+                     int groups, float eps, const void* x_bias, int xb_dtype, cudaStream_t stream);
 /* out = a N(z) + b N(z^2) + c N(z^3) + e with N(u) = u / sqrt(mean(u^2) + eps) over the row; coef [4] = (a, b, c, e). */
 PHOTON_EXPORT int photon_polynorm(const void* z, long z_stride, int z_dtype, const void* coef, int coef_dtype, void* out,
                      long out_stride, int out_dtype, int T, int F, float eps, cudaStream_t stream);

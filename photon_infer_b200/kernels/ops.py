@@ -1208,14 +1208,18 @@ GATE_MODES = {None: 0, "silu_before": 1, "sigmoid_after": 2}
 
 def group_rmsnorm(x: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, groups: int,
                   out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-                  gate: Optional[torch.Tensor] = None, gate_mode: Optional[str] = None) -> None:
+                  gate: Optional[torch.Tensor] = None, gate_mode: Optional[str] = None,
+                  x_bias: Optional[torch.Tensor] = None) -> None:
     """RMS norm in ``groups`` equal consecutive parts of a row: every part of ``x [T, H]`` (a view with a row stride) is
     divided by its own ``sqrt(mean(part^2) + eps)``, the whole times ``weight [H]``.  ``gate`` (float32 ``[T, H]`` view):
     ``gate_mode`` ``silu_before`` multiplies the row by ``silu(gate)`` before the norm, ``sigmoid_after`` the normed row by
     ``sigmoid(gate)``.  ``residual`` (contiguous float32 ``[T, H]``): the result is added to it in place, and ``out`` (may
     then be None) receives the stream's new rows in its own type; with ``x`` None ``out`` just receives the stream's rows.
-    Without a residual ``out`` receives the result."""
-    _cuda(x, weight, out, residual, gate)
+    Without a residual ``out`` receives the result.  ``x_bias [H]``: added to every row of ``x`` first (the bias of the
+    product that made ``x``, which then needs no pass of its own)."""
+    _cuda(x, weight, out, residual, gate, x_bias)
+    if x_bias is not None and (x is None or x_bias.numel() != x.shape[1] or not x_bias.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "group_rmsnorm: x_bias must be contiguous [H] and goes with x")
     ref = x if x is not None else residual
     if ref is None or (out is None and residual is None):
         raise PhotonError(ErrorCode.INVALID_ARGUMENT, "group_rmsnorm: nothing to read or nothing to write")
@@ -1234,11 +1238,12 @@ def group_rmsnorm(x: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "group_rmsnorm: the gate must be a float32 [T, H] view")
     f = _fn("row_norms", "photon_group_rmsnorm",
             [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int,
-             c_int, c_float, c_void_p])
+             c_int, c_float, c_void_p, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0) if x is not None else 0, _dtype_code(x) if x is not None else F32, _ptr(gate),
              gate.stride(0) if gate is not None else 0, GATE_MODES[gate_mode], _ptr(residual), _ptr(weight),
              _dtype_code(weight) if weight is not None else F32, _ptr(out), out.stride(0) if out is not None else 0,
-             _dtype_code(out) if out is not None else F32, T, H, int(groups), float(eps), _stream()), "group_rmsnorm")
+             _dtype_code(out) if out is not None else F32, T, H, int(groups), float(eps), _ptr(x_bias),
+             _dtype_code(x_bias) if x_bias is not None else F32, _stream()), "group_rmsnorm")
 
 
 def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:

@@ -180,10 +180,12 @@ class Normed:
     its sublayers' outputs).  A consumer that knows the kind does norm and sum in one kernel (``Norm.add_normed``)."""
     tensor: torch.Tensor
     norm: "Norm"
+    bias: Optional[torch.Tensor] = None     # [H]: still to be added to ``tensor`` before the norm (a product's bias)
 
     def materialize(self) -> torch.Tensor:
         """The normed rows as a 32-bit tensor, for a consumer that cannot take the norm into its own kernel."""
-        return self.norm.forward(self.tensor, torch.float32)
+        x = self.tensor if self.bias is None else self.tensor.to(torch.float32) + self.bias.to(torch.float32)
+        return self.norm.forward(x, torch.float32)
 
 
 def delta_terms(delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]:
@@ -222,10 +224,14 @@ class Norm(Part):
             residual.add_(d1.to(residual.dtype) + d2.to(residual.dtype) if d2 is not None else d1.to(residual.dtype))
         return self.forward(residual, out_dtype)
 
-    def add_normed(self, x: Optional[torch.Tensor], residual: torch.Tensor, out_dtype: Optional[torch.dtype]):
-        """``residual += forward(x)`` in 32-bit, in place (``x`` None: nothing is added); returns the stream's new rows
-        in ``out_dtype`` (None: nothing is returned).  A norm that sits on a sublayer's output fuses the three."""
+    def add_normed(self, x: Optional[torch.Tensor], residual: torch.Tensor, out_dtype: Optional[torch.dtype],
+                   bias: Optional[torch.Tensor] = None):
+        """``residual += forward(x + bias)`` in 32-bit, in place (``x`` None: nothing is added; ``bias [H]`` may be None);
+        returns the stream's new rows in ``out_dtype`` (None: nothing is returned).  A norm that sits on a sublayer's
+        output fuses them all."""
         if x is not None:
+            if bias is not None:
+                x = x.to(torch.float32) + bias.to(torch.float32)
             residual.add_(self.forward(x, torch.float32))
         if out_dtype is None:
             return None
@@ -258,6 +264,11 @@ class Mixer(Part):
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         """``h [T, H]`` normed input in the run dtype; returns ``[T, H]`` to add to the residual."""
         raise NotImplementedError
+
+    def forward_deferred_bias(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache):
+        """``(output, bias)``: like ``forward``, but a mixer whose output product has a bias may leave it out of the
+        output and hand it over, for a block whose next kernel adds it (``bias`` None: nothing is left out)."""
+        return self.forward(h, ctx, cache), None
 
     # Optional fast path.  A mixer that can take the residual sum and the norm into its first kernel
     # answers True and implements forward_with_norm; the block then skips the separate norm pass.

@@ -113,7 +113,7 @@ class OutputNormBlock(Block):
     def _enter(self, residual: torch.Tensor, delta, ctx: StepContext) -> torch.Tensor:
         """Adds what is pending and returns the stream's rows in the run type."""
         if isinstance(delta, Normed):
-            return delta.norm.add_normed(delta.tensor, residual, ctx.dtype)
+            return delta.norm.add_normed(delta.tensor, residual, ctx.dtype, bias=delta.bias)
         d1, d2 = delta_pair(delta)
         if d1 is not None:
             residual.add_(d1.to(residual.dtype) + d2.to(residual.dtype) if d2 is not None else d1.to(residual.dtype))
@@ -121,10 +121,10 @@ class OutputNormBlock(Block):
 
     def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
         h = self._enter(residual, delta, ctx)
-        a = self._mixer.forward(h, ctx, cache)
+        a, bias = self._mixer.forward_deferred_bias(h, ctx, cache)      # the output product's bias rides in the norm kernel
         if self.feed_forward is None:
-            return residual, Normed(a, self.norm1)
-        h2 = self.norm1.add_normed(a, residual, ctx.dtype)
+            return residual, Normed(a, self.norm1, bias)
+        h2 = self.norm1.add_normed(a, residual, ctx.dtype, bias=bias)
         return residual, Normed(self.feed_forward.forward(h2, ctx), self.norm2)
 
 

@@ -117,6 +117,12 @@ class DifferentialAttention(Mixer):
         return PagedCacheSpec(self.n_kv, 2 * self.head_dim, self.cache_window, value_dim=self.value_dim)
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        out, bias = self.forward_deferred_bias(h, ctx, cache)
+        if bias is not None:
+            ops.scale_bias_rows(out, 1.0, bias)
+        return out
+
+    def forward_deferred_bias(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache):
         T = h.shape[0]
         nq, nk, nv = self._sections
         rows = project(h, self.w_in, out_dtype=torch.float32)       # unrounded sums go into bias, norm and rotation
@@ -129,10 +135,7 @@ class DifferentialAttention(Mixer):
                       cache.v if store else None, self.n_q, self.n_kv, self.head_dim, self.value_dim, ctx.error_flag)
         attn = torch.empty((T, self.n_q * self.value_dim), dtype=h.dtype, device=h.device)
         self.attend(q, attn, ctx, cache)
-        out = project(attn, self.w_o, out_dtype=torch.float32)
-        if self.o_bias is not None:
-            ops.scale_bias_rows(out, 1.0, self.o_bias)
-        return out
+        return project(attn, self.w_o, out_dtype=torch.float32), self.o_bias
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
         """bfloat16 with sizes that are multiples of 16: the tensor-core kernel, for prompt portions and decoded tokens

@@ -119,19 +119,19 @@ class GroupRMSNorm(Norm):
         ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out=out)
         return out
 
-    def add_normed(self, x, residual, out_dtype):
+    def add_normed(self, x, residual, out_dtype, bias=None):
         if x is None and (out_dtype is None or out_dtype == residual.dtype):
             return residual if out_dtype is not None else None
         # the 32-bit run reads the stream itself; the bfloat16 run gets a rounded copy from the same kernel
         out = None if out_dtype in (None, residual.dtype) else torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
-        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out=out, residual=residual)
+        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out=out, residual=residual, x_bias=bias if x is not None else None)
         if out_dtype is None:
             return None
         return residual if out is None else out
 
     def add_forward(self, delta, residual, out_dtype):
         if isinstance(delta, Normed):
-            delta.norm.add_normed(delta.tensor, residual, None)
+            delta.norm.add_normed(delta.tensor, residual, None, bias=delta.bias)
         else:
             d1, d2 = delta_pair(delta)
             if d1 is not None:
@@ -142,7 +142,7 @@ class GroupRMSNorm(Norm):
         idx = rows.long()
         r = residual.index_select(0, idx)
         if isinstance(delta, Normed):
-            delta.norm.add_normed(delta.tensor.index_select(0, idx), r, None)
+            delta.norm.add_normed(delta.tensor.index_select(0, idx), r, None, bias=delta.bias)
         else:
             d = [x.index_select(0, idx) for x in delta_pair(delta) if x is not None]
             for x in d:

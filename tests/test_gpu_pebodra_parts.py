@@ -529,3 +529,39 @@ def test_block_with_norms_on_the_sublayers_outputs(dtype):
     x2 = x1 + plain.group_rms_norm(d, ws[1].double(), 3, 1e-5)
     x3 = x2 + plain.group_rms_norm(rnd(2 * rnd(x2) + 1), ws[0].double(), 3, 1e-5)
     assert rel_err(res2.cpu(), x3) < 5 * tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_mixer_s_output_bias_rides_in_the_norm_kernel(dtype):
+    """A mixer may hand its output product's bias over instead of adding it: the block's norm kernel adds it before the norm,
+    also when the output stays pending and when the model's last norm takes it on chosen rows."""
+    from photon_infer_b200.parts.base import Mixer, Normed, StepContext
+    from photon_infer_b200.parts.registry import create_part
+    W = 40
+    g = torch.Generator().manual_seed(4)
+    b = torch.randn(W, generator=g)
+
+    class WithBias(Mixer):
+        def forward(self, h, ctx, cache):
+            return 3 * h.float() + b.to(DEV)
+
+        def forward_deferred_bias(self, h, ctx, cache):
+            return 3 * h.float(), b.to(DEV)
+
+    norm = create_part("norm", "group_rms_norm", {"size": W, "eps": 1e-5, "groups": 4, "weight_name": "w"})
+    w = 1 + 0.2 * torch.randn(W, generator=g)
+    norm.load({"w": w.to(DEV)})
+    block = create_part("block", "output_norm", dict(norm1=norm, mixer=WithBias(), norm2=None, feed_forward=None))
+    x = torch.randn(6, W, generator=g)
+    ctx = StepContext(num_tokens=6, num_seqs=1, dtype=dtype, token_ids=None, positions=None, token_seq=None, cu_tokens=None,
+                      context_lens=None, state_slots=None, groups=[])
+    res, pending = block.forward(x.to(DEV).clone(), None, ctx, None)
+    assert isinstance(pending, Normed) and pending.bias is not None
+    want = x.double() + plain.group_rms_norm(3 * x.to(dtype).double() + b.double(), w.double(), 4, 1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert rel_err((res + pending.materialize()).cpu(), want) < tol
+    res2 = res.clone()
+    block._enter(res2, pending, ctx)
+    assert rel_err(res2.cpu(), want) < tol
+    rows = norm.add_forward_rows(pending, res, i32([5, 0]), torch.float32)
+    assert rel_err(rows.cpu(), plain.group_rms_norm(want[[5, 0]], w.double(), 4, 1e-5)) < tol
