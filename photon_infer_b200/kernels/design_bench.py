@@ -90,14 +90,14 @@ def pebodra_config(width: int, layers: int) -> dict:
     att_heads = max(1, width // 256)
     dense = dict(kind="dense", ff=4 * width)
     moe = dict(kind="moe", expert=dict(ff=width), router=dict(experts=16, top=2, groups=dict(count=4, keep=2)))
-    att = lambda extra: dict(heads=att_heads, kv_heads=max(1, att_heads // 4), dim=128, vdim=256, scale=128 ** -0.5, diff=0.3,
+    att = lambda extra: dict(heads=att_heads, kv_heads=max(1, att_heads // 4), dim=128, vdim=256, scale=128 ** -0.5, diff=0.2,
                              mask=dict(size=PEBODRA_WINDOW), rot=dict(base=10000.0, dims=64), **extra)
     kinds = [lambda i: dict(type="mlstm", mixer=dict(heads=heads, dim=128, vdim=128, gate_cap=15.0), mlp=dense),
              lambda i: dict(type="attention", mixer=att({}), mlp=moe),
              lambda i: dict(type="mamba2", mixer=dict(heads=heads, vdim=128, state=128, groups=max(1, heads // 8), conv=4,
                                                       norm_groups=max(1, heads // 8)), mlp=moe),
              lambda i: dict(type="attention", mixer=att(dict(kv_from=i - 2)), mlp=dense)]
-    return dict(architecture="Pebodra", vocab=32000, width=width, norm=dict(eps=1e-6, groups=4), logit_softcap=30.0,
+    return dict(architecture="Pebodra", vocab=32000, width=width, norm=dict(eps=1e-5, groups=8), logit_softcap=50.0,
                 layers=[kinds[i % 4](i) for i in range(layers)])
 
 

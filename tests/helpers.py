@@ -465,9 +465,9 @@ TINY_PEBODRA: Dict[str, dict] = {
     # heads of 64 and 128; a window longer than most requests; pages of 32; one head
     "pb_d": dict(
         config=dict(architecture="Pebodra", vocab=90, width=32, norm=dict(eps=1e-5, groups=2), logit_softcap=50.0,
-                    layers=[dict(type="attention", mixer=_patt(2, 1, 64, 128, 0.09, 0.3, 100, (300000.0, 64)), mlp=_dense(24)),
+                    layers=[dict(type="attention", mixer=_patt(2, 1, 64, 128, 0.09, 0.45, 100, (300000.0, 64)), mlp=_dense(24)),
                             dict(type="mamba2", mixer=_pssm(2, 64, 128, 1, 4, 2), mlp=_pmoe(2, 2, 16)),
-                            dict(type="mlstm", mixer=_pmem(1, 128, 128, 12.0), mlp=_dense(48))]),
+                            dict(type="mlstm", mixer=_pmem(1, 128, 128, 10.0), mlp=_dense(48))]),
         seed=44, init_std=0.15, norm_std=0.1, block_size=16),
     # two layers read the first one's keys and values, one of them without a window (so everything is kept); a
     # convolution of one tap (no rows to carry); a small bound on the gates; groups of two experts, one kept

@@ -38,7 +38,7 @@ def _weights(part, dtype, std, seed, overrides=None):
 # ----------------------------------------------------------------------------- norms
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,groups", [(72, 4), (50, 5), (1024, 1), (96, 16), (60, 60), (320, 2)])
+@pytest.mark.parametrize("width,groups", [(72, 4), (50, 5), (1024, 1), (96, 16), (60, 60), (336, 2)])
 def test_group_norm_of_rows_and_on_a_sublayer_s_output(dtype, width, groups):
     from photon_infer_b200.parts.registry import create_part
     g = torch.Generator().manual_seed(width + groups)
@@ -111,8 +111,8 @@ def test_bounded_logits():
     from photon_infer_b200.kernels import ops
     x = torch.linspace(-200, 200, 1001)
     y = x.to(DEV).clone()
-    ops.softcap_(y, 30.0)
-    assert rel_err(y.cpu(), 30.0 * torch.tanh(x.double() / 30.0)) < 1e-6
+    ops.softcap_(y, 25.0)
+    assert rel_err(y.cpu(), 25.0 * torch.tanh(x.double() / 25.0)) < 1e-6
 
 
 # ----------------------------------------------------------------------------- router
@@ -250,8 +250,8 @@ class _Cached:
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,dv,page,window", [(4, 2, 16, 24, 16, 40), (3, 1, 48, 96, 8, None), (2, 2, 64, 128, 32, 100), (5, 5, 6, 10, 16, 3),
-                                                  (8, 1, 128, 128, 16, 136), (2, 1, 10, 7, 4, 33)])
+@pytest.mark.parametrize("H,G,d,dv,page,window", [(4, 2, 16, 24, 16, 40), (3, 1, 48, 80, 8, None), (2, 2, 64, 128, 32, 100), (5, 5, 6, 10, 16, 3),
+                                                  (8, 1, 128, 128, 16, 130), (2, 1, 10, 7, 4, 33)])
 def test_attention_prompts_decoding_and_batches(dtype, H, G, d, dv, page, window):
     lengths, counts = [150, 37, 64, 1, 200], [150, 1, 20, 1, 2]
     c = _Cached(lengths, counts, H, G, d, dv, page, dtype, seed=H * d, std=0.7)
@@ -259,8 +259,8 @@ def test_attention_prompts_decoding_and_batches(dtype, H, G, d, dv, page, window
     assert rel_err(got, want) < (2e-5 if dtype == torch.float32 else 2e-2)
 
 
-@pytest.mark.parametrize("H,G,d,dv,page,window", [(4, 2, 16, 32, 16, 40), (3, 1, 48, 96, 8, None), (2, 2, 64, 128, 32, 100), (5, 5, 32, 16, 16, 3),
-                                                  (8, 1, 128, 128, 16, 136), (8, 2, 128, 256, 16, 70), (6, 2, 16, 48, 4, 33)])
+@pytest.mark.parametrize("H,G,d,dv,page,window", [(4, 2, 16, 32, 16, 40), (3, 1, 48, 80, 8, None), (2, 2, 64, 128, 32, 100), (5, 5, 32, 16, 16, 3),
+                                                  (8, 1, 128, 128, 16, 130), (8, 2, 128, 256, 16, 70), (6, 2, 16, 48, 4, 33)])
 def test_attention_on_the_tensor_cores(H, G, d, dv, page, window):
     lengths, counts = [150, 37, 64, 1, 200, 300], [150, 1, 20, 1, 2, 129]
     c = _Cached(lengths, counts, H, G, d, dv, page, torch.bfloat16, seed=H * d + 1, std=0.7)
@@ -411,7 +411,7 @@ def _run_recurrence(mode, H, Gq, N, dv, lengths, cuts, seed, slots_total=3):
     return [torch.cat(x) for x in got], data, (p0.double(), p1.double(), p2.double())
 
 
-SHAPES = [(4, 2, 16, 8), (3, 3, 7, 11), (2, 1, 48, 48), (1, 1, 128, 40), (2, 2, 40, 15), (6, 2, 12, 4), (1, 1, 200, 17), (1, 1, 300, 9),
+SHAPES = [(4, 2, 16, 8), (3, 3, 7, 11), (2, 1, 56, 24), (1, 1, 128, 40), (2, 2, 40, 15), (6, 2, 12, 4), (1, 1, 200, 17), (1, 1, 300, 9),
           (1, 1, 512, 16)]
 
 
@@ -432,7 +432,7 @@ def test_state_space_recurrence_in_portions_batches_and_reused_slots(H, Gq, N, d
         assert torch.equal(got[r], whole[r]), r                 # the cut changes no bit
 
 
-@pytest.mark.parametrize("H,Gq,N,dv", [s for s in SHAPES if s[0] == s[1]] + [(4, 4, 16, 8), (2, 2, 48, 48)])
+@pytest.mark.parametrize("H,Gq,N,dv", [s for s in SHAPES if s[0] == s[1]] + [(4, 4, 16, 8), (2, 2, 72, 24)])
 def test_matrix_memory_recurrence_in_portions_batches_and_reused_slots(H, Gq, N, dv):
     lengths = [70, 33, 121, 18, 50]
     got, data, (bi, bf, _) = _run_recurrence("matrix_memory", H, Gq, N, dv, lengths, [[70], [1, 2, 16, 5], [17, 31, 3], [2], [1]], seed=N * dv)
@@ -463,12 +463,12 @@ def test_matrix_memory_keeps_its_exponentials_in_range():
     out = torch.empty(L, H * dv, dtype=torch.float32, device=DEV)
     rd = rows.to(DEV)
     ops.linrec("matrix_memory", rd[:, :H * N], rd[:, H * N:2 * H * N], rd[:, 2 * H * N:c], rd[:, c:c + H], rd[:, c + H:], bias.to(DEV),
-               bias.to(DEV), None, 12.0, 0.25, i32([0, L]), i32([0]), state, out, 1, H, H, N, dv, None)
+               bias.to(DEV), None, 9.0, 0.25, i32([0, L]), i32([0]), state, out, 1, H, H, N, dv, None)
     r = rows.double()
     want = plain.matrix_memory(r[:, :H * N].reshape(L, H, N) * 0.25, r[:, H * N:2 * H * N].reshape(L, H, N), r[:, 2 * H * N:c].reshape(L, H, dv),
-                               plain.capped(r[:, c:c + H], 12.0), torch.nn.functional.logsigmoid(plain.capped(r[:, c + H:], 12.0)))
+                               plain.capped(r[:, c:c + H], 9.0), torch.nn.functional.logsigmoid(plain.capped(r[:, c + H:], 9.0)))
     assert torch.isfinite(out).all() and rel_err(out.cpu(), want.reshape(L, H * dv)) < 5e-5
-    assert abs(float(state[0, -1]) - 12.0) < 1e-3               # the running maximum is kept with the state
+    assert abs(float(state[0, -1]) - 9.0) < 1e-3               # the running maximum is kept with the state
 
 
 def test_a_negative_slot_starts_from_zero_and_stores_nothing():
