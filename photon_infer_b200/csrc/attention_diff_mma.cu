@@ -11,6 +11,7 @@
 // head's norm over its DV numbers, one rounding.  The key tiles start at a multiple of 64 at or below the first key
 // that the block's first token sees, so a token's sums depend on its place in the block, which is why this kernel
 // serves the bfloat16 run only (its float32 run keeps the general kernel, whose sums depend on the position alone).
+// Decode steps share a token's key tiles out over several blocks; a second kernel puts the shares together.
 #include "common.cuh"
 #include <math.h>
 #include <mma.h>
@@ -62,7 +63,7 @@ diff_mma_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ ou
                 const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const int* __restrict__ block_table,
                 int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ positions, int num_seqs, int n_q,
                 int n_kv, int page_size, int num_pages, int window, float scale, float lambda, float out_scale, float eps,
-                int tokens_per_block, int* err) {
+                int tokens_per_block, int splits, float* __restrict__ part, int* err) {
   constexpr int D = DIFF_D, DV = DIFF_DV, D2 = 2 * DIFF_D;
   extern __shared__ __align__(128) unsigned char dm_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(dm_raw);                       // [64][2 D]
@@ -90,7 +91,13 @@ diff_mma_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ ou
   const int rows = ntok * GH;                                       // rows in use: (token, head of the group)
   const int p_first = positions[tok0], p_last = positions[tok0 + ntok - 1];
   const int kmin = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
-  const int tile_lo = kmin / DM_KT, tile_hi = p_last / DM_KT + 1;
+  int tile_lo = kmin / DM_KT, tile_hi = p_last / DM_KT + 1;
+  if (splits > 1) {
+    // this block's share of the key tiles; the shares of a row meet in diff_merge_kernel, in the order of the shares
+    const int per = (tile_hi - tile_lo + splits - 1) / splits;
+    tile_lo += blockIdx.z * per;
+    tile_hi = min(tile_hi, tile_lo + per);
+  }
   const int* table = block_table + (size_t)s * max_pages;
 
   for (int r = tid; r < DM_ROWS; r += DM_THREADS) row_pos[r] = r < rows ? positions[tok0 + r / GH] : -1;
@@ -140,10 +147,9 @@ diff_mma_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ ou
   for (int n = 0; n < DV / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
-  load_tile(tile_lo, 0);
+  if (tile_lo < tile_hi) load_tile(tile_lo, 0);
   __syncthreads();                                                  // krow, row_pos and Qs are written
-  copy_tile(0);
-  dm_commit();
+  if (tile_lo < tile_hi) { copy_tile(0); dm_commit(); }
   const int p_lo = row_pos[r_lo], p_hi = row_pos[r_hi];
   const float sl2 = scale * 1.4426950408889634f;                    // scores in units of log 2
   for (int kt = tile_lo; kt < tile_hi; ++kt) {
@@ -228,6 +234,21 @@ diff_mma_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ ou
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if (splits > 1) {
+    // a share of the keys: the sums as they stand, with the running maximum (in units of log 2) and denominator behind them
+    const int n_rows[2] = {r_lo, r_hi};
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = n_rows[half];
+      if (r >= rows) continue;
+      float* dst = part + ((((size_t)(tok0 + r / GH) * n_q + (g * GH + r % GH)) * 2 + mp) * splits + blockIdx.z) * (DV + 2);
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n)
+        *reinterpret_cast<float2*>(dst + n * 8 + (lane & 3) * 2) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
+      if ((lane & 3) == 0) { dst[DV] = half ? m_hi : m_lo; dst[DV + 1] = half ? l_hi : l_lo; }
+    }
+    return;
+  }
   __syncthreads();                                                  // the stages are free: the maps' outputs go there
   {
     const float i_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, i_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
@@ -254,18 +275,57 @@ diff_mma_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ ou
   }
 }
 
+// The shares of one (token, head) put together, in the order of the shares, for both maps; then the difference of the
+// maps and the head's norm.
+__global__ void __launch_bounds__(128)
+diff_merge_kernel(const float* __restrict__ part, int splits, bf16* __restrict__ out, long out_stride, int n_q, float lambda,
+                  float out_scale, float eps) {
+  constexpr int DV = DIFF_DV;
+  __shared__ float a[2][DIFF_DV];
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y;
+  for (int mp = 0; mp < 2; ++mp) {
+    const float* src = part + (((size_t)t * n_q + h) * 2 + mp) * splits * (DV + 2);
+    float m = -INFINITY;
+    for (int z = 0; z < splits; ++z) m = fmaxf(m, src[z * (DV + 2) + DV]);
+    float l = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = src[z * (DV + 2) + DV];
+      if (mz != -INFINITY) l += src[z * (DV + 2) + DV + 1] * exp2f(mz - m);
+    }
+    for (int j = threadIdx.x; j < DV; j += blockDim.x) {
+      float acc = 0.f;
+      for (int z = 0; z < splits; ++z) {
+        const float mz = src[z * (DV + 2) + DV];
+        if (mz != -INFINITY) acc += src[z * (DV + 2) + j] * exp2f(mz - m);
+      }
+      a[mp][j] = l > 0.f ? acc / l : 0.f;
+    }
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < DV; j += blockDim.x) { const float x = a[0][j] - lambda * a[1][j]; ss += x * x; }
+  ss = block_sum(ss, red);
+  const float inv = out_scale / sqrtf(ss / (float)DV + eps);
+  bf16* dst = out + (size_t)t * out_stride + (size_t)h * DV;
+  for (int j = threadIdx.x; j < DV; j += blockDim.x) dst[j] = __float2bfloat16_rn((a[0][j] - lambda * a[1][j]) * inv);
+}
+
 PHOTON_API int photon_diff_mma_dims(void) { return DIFF_D * 65536 + DIFF_DV; }
 
 // q [T][n_q * 2 D] bfloat16 (row stride q_stride, 16-byte aligned rows), out [T][n_q * DV]; k_cache [pages][n_kv][page_size][2 D],
 // v_cache [pages][n_kv][page_size][DV].  cu_tokens [S + 1]: the first token of every request of the step; a request's
 // tokens have consecutive positions.  window <= 0: all keys.  tiles: an upper bound of sum over requests of
-// ceil(tokens / tokens_per_block), tokens_per_block = 64 / (n_q / n_kv).
+// ceil(tokens / tokens_per_block), tokens_per_block = 64 / (n_q / n_kv).  splits > 1 (decode steps, where a block per
+// (token tile, key/value head) leaves the GPU empty): every block's key tiles are shared out over that many blocks, which
+// leave their shares in part (float [T * n_q * 2 * splits * (DV + 2)], T the step's tokens) for a second kernel to put together.
 PHOTON_API int photon_diff_mma(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                                const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
                                const int* positions, int num_seqs, int tiles, int n_q, int n_kv, int page_size, int num_pages,
-                               int window, float scale, float lambda, float out_scale, float eps, int* err,
-                               cudaStream_t stream) {
+                               int window, float scale, float lambda, float out_scale, float eps, int splits, float* part,
+                               int num_tokens, int* err, cudaStream_t stream) {
   if (num_seqs <= 0 || tiles <= 0) return 0;
+  if (splits < 1 || splits > 64 || (splits > 1 && (part == nullptr || num_tokens <= 0 || n_q > 65535))) return PHOTON_ERR_ARGUMENT;
   if (n_kv <= 0 || n_q <= 0 || n_q % n_kv || page_size <= 0) return PHOTON_ERR_ARGUMENT;
   const int GH = n_q / n_kv;
   if (GH > DM_ROWS || n_kv > 65535) return PHOTON_ERR_UNSUPPORTED;
@@ -276,8 +336,12 @@ PHOTON_API int photon_diff_mma(const void* q, long q_stride, void* out, long out
   if (smem > 220 * 1024) return PHOTON_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(diff_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  diff_mma_kernel<<<dim3(tiles, n_kv), DM_THREADS, smem, stream>>>(
+  diff_mma_kernel<<<dim3(tiles, n_kv, splits), DM_THREADS, smem, stream>>>(
       (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages,
-      cu_tokens, positions, num_seqs, n_q, n_kv, page_size, num_pages, window, scale, lambda, out_scale, eps, DM_ROWS / GH, err);
+      cu_tokens, positions, num_seqs, n_q, n_kv, page_size, num_pages, window, scale, lambda, out_scale, eps, DM_ROWS / GH,
+      splits, part, err);
+  int st = launch_status();
+  if (st != 0 || splits <= 1) return st;
+  diff_merge_kernel<<<dim3(num_tokens, n_q), 128, 0, stream>>>(part, splits, (bf16*)out, out_stride, n_q, lambda, out_scale, eps);
   return launch_status();
 }

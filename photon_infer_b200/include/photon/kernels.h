@@ -223,11 +223,13 @@ PHOTON_EXPORT int photon_diff_attention(const void* q, long q_stride, void* out,
 /* ------------------------------------------------------------------ attention_diff_mma.cu (-DDIFF_D=d -DDIFF_DV=dv, multiples of 16; bfloat16) */
 PHOTON_EXPORT int photon_diff_mma_dims(void);                    /* d * 65536 + dv of this build */
 /* photon_diff_attention on the tensor cores.  cu_tokens [S + 1]: the first token of every request of the step (a request's
- * tokens have consecutive positions); tiles: sum over the requests of ceil(tokens / (64 / (n_q / n_kv))). */
+ * tokens have consecutive positions); tiles: sum over the requests of ceil(tokens / (64 / (n_q / n_kv))).  splits > 1: the key
+ * tiles of every block are shared out over that many blocks and put together by a second kernel; part: float scratch of
+ * num_tokens * n_q * 2 * splits * (dv + 2). */
 PHOTON_EXPORT int photon_diff_mma(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
                      const int* block_table, int max_pages, const int* cu_tokens, const int* positions, int num_seqs, int tiles,
                      int n_q, int n_kv, int page_size, int num_pages, int window, float scale, float lambda, float out_scale,
-                     float eps, int* err, cudaStream_t stream);
+                     float eps, int splits, float* part, int num_tokens, int* err, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ linrec.cu: recurrences with one decay per head and token */
 /* y float [T][C] = silu(bias + causal convolution over `taps` tokens per channel) of x [T][>= C] (x_dtype); taps_w float

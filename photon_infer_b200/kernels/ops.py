@@ -1359,9 +1359,11 @@ def diff_mma_supported(dtype: torch.dtype, heads: int, kv_heads: int, dim: int, 
 def diff_attention_mma(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                        cu_tokens: torch.Tensor, positions: torch.Tensor, query_lens, heads: int, kv_heads: int, dim: int,
                        value_dim: int, window: Optional[int], scale: float, lam: float, out_scale: float, eps: float,
-                       err: Optional[torch.Tensor]) -> None:
+                       err: Optional[torch.Tensor], splits: int = 1) -> None:
     """``diff_attention`` on the tensor cores (bfloat16): a block owns the query heads of one key/value head for up to
-    ``64 / (heads / kv_heads)`` neighbouring tokens of a request.  ``query_lens``: the requests' token counts (host)."""
+    ``64 / (heads / kv_heads)`` neighbouring tokens of a request.  ``query_lens``: the requests' token counts (host).
+    ``splits`` > 1 shares every block's key tiles out over that many blocks (decode steps); a second kernel puts the
+    shares together in their order."""
     _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, err)
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
@@ -1377,11 +1379,17 @@ def diff_attention_mma(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor
     tiles = sum(-(-int(n) // per_block) for n in query_lens)
     f = _fn("attention_diff_mma", "photon_diff_mma",
             [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_void_p, c_void_p], defines={"DIFF_D": dim, "DIFF_DV": value_dim})
+             c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p],
+            defines={"DIFF_D": dim, "DIFF_DV": value_dim})
+    splits = max(1, min(int(splits), 64))
+    part = talk_scratch(q.device, T * heads * 2 * splits * (value_dim + 2)) if splits > 1 else None
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(cu_tokens), _ptr(positions), len(query_lens), tiles, heads, kv_heads, k_cache.shape[2], k_cache.shape[0],
-             int(window) if window else 0, float(scale), float(lam), float(out_scale), float(eps), _ptr(err), _stream()),
-           "diff_attention_mma")
+             int(window) if window else 0, float(scale), float(lam), float(out_scale), float(eps), splits, _ptr(part), T, _ptr(err),
+             _stream()), "diff_attention_mma")
+    if splits > 1:
+        global _launch_count
+        _launch_count += 1
 
 
 # ----------------------------------------------------------------------------- recurrences with one decay per head and token

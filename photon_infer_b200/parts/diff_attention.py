@@ -142,9 +142,15 @@ class DifferentialAttention(Mixer):
         alike.  float32 and other sizes: the general kernel, whose sums depend on a token's position alone."""
         group = ctx.groups[cache.group]
         if self._mma_ok(q.dtype) and q.stride(0) % 8 == 0 and ctx.host_query_lens:
+            splits = 1
+            if ctx.max_query_len == 1:
+                # a decode step: a block per (request, key/value head) leaves most SMs empty, so the keys are shared out
+                keys = ctx.max_context_len if self.window is None else min(self.window + 1, ctx.max_context_len)
+                blocks = max(1, ctx.num_seqs * self.n_kv)
+                splits = max(1, min(-(-keys // 128), ops.sm_count(q.device) // blocks, 16))
             ops.diff_attention_mma(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions, ctx.host_query_lens,
                                    self.n_q, self.n_kv, self.head_dim, self.value_dim, self.window, self.scale, self.lam,
-                                   1.0 - self.diff, self.eps, ctx.error_flag)
+                                   1.0 - self.diff, self.eps, ctx.error_flag, splits=splits)
             return
         ops.diff_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions, self.n_q, self.n_kv,
                            self.head_dim, self.value_dim, self.window, self.scale, self.lam, 1.0 - self.diff, self.eps,

@@ -207,7 +207,7 @@ class _Cached:
         self.v = [torch.randn(L, G, dv, generator=g).to(dtype) for L in lengths]
         self.q = [(std * torch.randn(n, H, 2, d, generator=g)).to(dtype) for n in counts]
 
-    def run(self, window, scale, lam, diff, eps=1e-5, mma=False):
+    def run(self, window, scale, lam, diff, eps=1e-5, mma=False, splits=1):
         from photon_infer_b200.kernels import ops
         H, G, d, dv = self.dims
         page = self.page
@@ -236,7 +236,7 @@ class _Cached:
             for n in self.counts:
                 cu.append(cu[-1] + n)
             ops.diff_attention_mma(q, out, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(cu), i32(pos), self.counts, H, G, d, dv, window,
-                                   scale, lam, 1.0 - diff, eps, err)
+                                   scale, lam, 1.0 - diff, eps, err, splits=splits)
         else:
             ops.diff_attention(q, out, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(tseq), i32(pos), H, G, d, dv, window, scale, lam,
                                1.0 - diff, eps, err)
@@ -268,6 +268,33 @@ def test_attention_on_the_tensor_cores(H, G, d, dv, page, window):
     assert rel_err(got, want) < 2e-2
     general, _ = c.run(window, d ** -0.5, 0.37, 0.2)
     assert rel_err(got, general.double()) < 2e-2
+
+
+@pytest.mark.parametrize("splits", [2, 3, 7, 16])
+@pytest.mark.parametrize("H,G,d,dv,page,window", [(4, 2, 16, 32, 16, 40), (8, 2, 128, 256, 16, None), (3, 1, 48, 80, 8, 300), (2, 2, 64, 128, 32, 100)])
+def test_decoded_tokens_with_their_keys_shared_out_over_blocks(splits, H, G, d, dv, page, window):
+    """Single tokens of requests of very different lengths (one key, a page, many tiles): shares without any key, shares
+    of one tile and the merge in the order of the shares."""
+    lengths = [700, 1, 64, 65, 17, 400, 129]
+    c = _Cached(lengths, [1] * len(lengths), H, G, d, dv, page, torch.bfloat16, seed=splits + d, std=0.7)
+    got, want = c.run(window, d ** -0.5, 0.4, 0.25, mma=True, splits=splits)
+    assert rel_err(got, want) < 2e-2
+    whole, _ = c.run(window, d ** -0.5, 0.4, 0.25, mma=True)
+    assert rel_err(got, whole.double()) < 1e-2
+
+
+@pytest.mark.parametrize("which_map", [0, 1])
+def test_a_key_that_stands_out_when_the_keys_are_shared_out(which_map):
+    H, G, d, dv, page, window, L = 2, 1, 32, 16, 16, 150, 430
+    for place in (L - 1, L - window, L - window - 1, L - window + 1, 0, 300, 319, 320, 383, 384, 385):
+        c = _Cached([L], [1], H, G, d, dv, page, torch.bfloat16, seed=place + 1, std=0.05)
+        direction = torch.zeros(d)
+        direction[3] = 4.0
+        c.k[0][place, 0, which_map] = direction.bfloat16()
+        c.q[0][-1, :, which_map] = (3 * direction).bfloat16()
+        c.v[0][place] = 25.0
+        got, want = c.run(window, 1.0, 0.6, 0.1, mma=True, splits=3)
+        assert rel_err(got, want) < 3e-2, place
 
 
 @pytest.mark.parametrize("which_map", [0, 1])
